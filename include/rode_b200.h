@@ -1,0 +1,138 @@
+/*
+ * rode_b200 — C ABI of the RoDe hot path (row-decomposition preprocessing, SpMM, SDDMM)
+ * for NVIDIA B200 (sm_100a).  Shared library: librode_b200.so.
+ *
+ * Plain C: pointers, ints and sizes only.  Every function returns a status code
+ * (RODE_OK == 0) and never throws, prints or exits; rode_last_error() gives a
+ * thread-local message for the last non-zero status.  All data pointers are DEVICE
+ * pointers unless the name ends in _cpu / says "host".  Launches are asynchronous on the
+ * streams passed in; a null stream means the CUDA default stream.
+ *
+ * Each entry point names the interface of the reference project (Da1sypetals/rode,
+ * file:line inside that project) that it stands in for.  The C++ signatures of the
+ * reference itself are declared in RoDeSpmm.h, RoDeSddmm.h and RoDePreprocess.h beside
+ * this file and are thin wrappers over the functions below.
+ *
+ * Array contract shared by all compute calls (same as the reference):
+ *   row_offsets   int32[M+1]   CSR row pointer
+ *   column_indices int32[nnz], values T[nnz]
+ *   block_r_ind   int32[m1]    row of every block segment          (preprocess output)
+ *   st_off        int32[m1+1]  first nonzero of every segment; st_off[m1] is an end
+ *                              sentinel (any value >= row_offsets[M]); this library never
+ *                              reads st_off[m1]
+ *   residue_r_ind int32[m2]    rows that own a residue             (preprocess output)
+ * The metadata must be what the preprocessing produces for the same row_offsets.
+ */
+#ifndef RODE_B200_H_
+#define RODE_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without pulling in the CUDA headers. */
+typedef struct CUstream_st *rode_stream_t;
+
+enum rode_status {
+    RODE_OK = 0,
+    RODE_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, unsupported width, ... */
+    RODE_ERR_WORKSPACE = 2,        /* workspace missing or too small                      */
+    RODE_ERR_CUDA = 3,             /* a CUDA runtime call or a launch failed              */
+    RODE_ERR_NO_DEVICE = 4         /* no usable sm_100 device                             */
+};
+
+/* Message for the last non-zero status returned on this thread ("" if none). */
+const char *rode_last_error(void);
+
+/* Library version, "major.minor.patch". */
+const char *rode_version(void);
+
+/* ------------------------------------------------------------------------------------
+ * Row-decomposition preprocessing.
+ *
+ * rode_preprocess replaces RoDe_preprocess (Preprocess_opt/_preprocess.cu:323-339: count
+ * kernel, two CUB scans, fill kernel).  Results are bit-identical to the reference's
+ * specification loop RoDe_preprocess_cpu (Preprocess_opt/_preprocess.cu:340-373), and the
+ * end sentinel st_off[n_blk] = row_ptr[M] of the reference's host copies
+ * (RoDe_SDDMM/main.cu:162) is written too.
+ *
+ *   seg_len  nonzeros per block segment (512; 32 for SDDMM with K = 128)
+ *   k_block  smallest block-part length (32); seg_len % k_block == 0
+ *   vec_len  alignment unit of row starts (4); k_block % vec_len == 0
+ *   row_ptr  int32[M+1] device
+ *   block_r_ind, st_off   device, capacity >= n_blk (+1 for st_off); the bound
+ *                         rode_preprocess_capacity() is always enough
+ *   residue_r_ind         device, capacity >= min(M, n_res)
+ *   n_blk, n_res          device int32[1] each
+ *   workspace             device scratch of rode_preprocess_workspace_bytes(M) bytes,
+ *                         256-byte aligned; contents are don't-care before and after
+ * Unlike the reference, outputs are never used as scratch, so there is no in-place
+ * hazard between thread blocks.
+ */
+int rode_preprocess_workspace_bytes(int M, size_t *bytes);
+
+/* Upper bound of n_blk for a matrix of M rows and nnz nonzeros (host arithmetic only):
+ * (nnz + (vec_len-1)*M) / seg_len + M. */
+int rode_preprocess_capacity(int seg_len, int vec_len, int M, long long nnz, long long *max_blocks);
+
+int rode_preprocess(int seg_len, int k_block, int vec_len, int M, const int *row_ptr,
+                    int *block_r_ind, int *st_off, int *residue_r_ind, int *n_blk, int *n_res,
+                    void *workspace, size_t workspace_bytes, rode_stream_t stream);
+
+/* Host twin with HOST pointers, replacing RoDe_preprocess_cpu
+ * (Preprocess_opt/_preprocess.cu:340-373) and the host loops of
+ * RoDe_SDDMM/main.cu:114-163.  Part of the reference's API surface; it is not a fallback
+ * for the device path and nothing in this library calls it. */
+int rode_preprocess_cpu(int seg_len, int k_block, int vec_len, int M, const int *row_ptr,
+                        int *block_r_ind, int *st_off, int *residue_r_ind, int *n_blk, int *n_res);
+
+/* ------------------------------------------------------------------------------------
+ * SpMM:  C[M x n] = S[M x k] * B[k x n], S in CSR + RoDe metadata, B and C row-major.
+ *
+ * Replaces RoDeSpmm_n32 / RoDeSpmm_n128 (RoDe_SpMM/RoDeSpmm.h:4-14, launcher
+ * RoDe_SpMM/RoDeSpmm.cu:492-529).  One call serves every width: n must be a multiple of
+ * 32 elements for float, 16 for double.  Block segments run on stream1, pure-residue rows
+ * on stream2; the caller synchronises both, as with the reference.
+ *
+ * Differences a caller can observe: every row that appears in block_r_ind or
+ * residue_r_ind is WRITTEN (not accumulated), without floating-point atomics, so results
+ * are deterministic and C needs zero-filling only for the rows in neither list (empty rows
+ * at an aligned offset), exactly the rows the reference never touches.
+ *
+ * Rows split over several segments are summed through `workspace`
+ * (rode_spmm_workspace_bytes(m1, n, sizeof(T)) bytes, 256-byte aligned, may be null when
+ * that size is 0).  Column byte offsets are formed in 64 bits.
+ */
+int rode_spmm_workspace_bytes(int m1, int n, int elem_size, size_t *bytes);
+
+int rode_spmm_f32(int m1, int m2, int k, int n, const float *values, const int *column_indices,
+                  const int *row_offsets, const int *block_r_ind, const int *residue_r_ind,
+                  const int *st_off, const float *B, float *C, void *workspace,
+                  size_t workspace_bytes, rode_stream_t stream1, rode_stream_t stream2);
+
+int rode_spmm_f64(int m1, int m2, int k, int n, const double *values, const int *column_indices,
+                  const int *row_offsets, const int *block_r_ind, const int *residue_r_ind,
+                  const int *st_off, const double *B, double *C, void *workspace,
+                  size_t workspace_bytes, rode_stream_t stream1, rode_stream_t stream2);
+
+/* ------------------------------------------------------------------------------------
+ * SDDMM:  out[e] = values[e] * dot(lhs[row(e), 0:k], rhs[col(e), 0:k]) for every stored e.
+ *
+ * Replaces RoDeSDDMM_n32 / RoDeSDDMM_n128 (RoDe_SDDMM/RoDeSddmm.h:4-9, launchers
+ * RoDe_SDDMM/RoDeSddmm.cu:496-545).  k in {32, 64, 128} (the reference has 32 and 128);
+ * lhs is [M x k], rhs is [n x k], both row-major; out is fp32[nnz] aligned with values.
+ * Block segments run on stream1, pure-residue rows on stream2.  A null stream is the
+ * default stream (the reference silently skips a kernel whose stream handle is null,
+ * RoDeSddmm.cu:503,509; this library does not).  Needs no workspace.
+ */
+int rode_sddmm_f32(int m1, int m2, int n, int k, const int *block_r_ind, const int *residue_r_ind,
+                   const int *st_off, const int *row_offsets, const int *column_indices,
+                   const float *values, const float *lhs, const float *rhs, float *out,
+                   rode_stream_t stream1, rode_stream_t stream2);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RODE_B200_H_ */

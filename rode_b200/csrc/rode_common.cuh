@@ -1,0 +1,115 @@
+// Shared host/device helpers of librode_b200 (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "rode_b200.h"
+
+namespace rode {
+
+// Thread-local message behind rode_last_error().
+char *error_buffer();
+int fail(int status, const char *fmt, ...);
+
+#define RODE_CUDA_TRY(expr)                                                                 \
+    do {                                                                                    \
+        cudaError_t rode_err_ = (expr);                                                     \
+        if (rode_err_ != cudaSuccess)                                                       \
+            return ::rode::fail(RODE_ERR_CUDA, "%s failed: %s", #expr,                      \
+                                cudaGetErrorString(rode_err_));                             \
+    } while (0)
+
+// Launch check that does not clear a sticky error and does not synchronise.
+#define RODE_CHECK_LAUNCH(what)                                                             \
+    do {                                                                                    \
+        cudaError_t rode_err_ = cudaPeekAtLastError();                                      \
+        if (rode_err_ != cudaSuccess)                                                       \
+            return ::rode::fail(RODE_ERR_CUDA, "launch of %s failed: %s", what,             \
+                                cudaGetErrorString(rode_err_));                             \
+    } while (0)
+
+inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<size_t>(p) % a) == 0; }
+
+// ---------------------------------------------------------------------------------------
+// Device-side vector types: one 16-byte load per lane for either scalar type.
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+    using type = float4;
+    static constexpr int kLen = 4;
+};
+template <>
+struct Vec16<double> {
+    using type = double2;
+    static constexpr int kLen = 2;
+};
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float4 vzero(float4 *) { return make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ double2 vzero(double2 *) { return make_double2(0.0, 0.0); }
+
+__device__ __forceinline__ void vfma(float4 &acc, float s, const float4 &b) {
+    acc.x = fmaf(s, b.x, acc.x);
+    acc.y = fmaf(s, b.y, acc.y);
+    acc.z = fmaf(s, b.z, acc.z);
+    acc.w = fmaf(s, b.w, acc.w);
+}
+__device__ __forceinline__ void vfma(double2 &acc, double s, const double2 &b) {
+    acc.x = fma(s, b.x, acc.x);
+    acc.y = fma(s, b.y, acc.y);
+}
+
+__device__ __forceinline__ float4 vshfl_xor(unsigned mask, const float4 &v, int lane_mask) {
+    return make_float4(__shfl_xor_sync(mask, v.x, lane_mask), __shfl_xor_sync(mask, v.y, lane_mask),
+                       __shfl_xor_sync(mask, v.z, lane_mask), __shfl_xor_sync(mask, v.w, lane_mask));
+}
+__device__ __forceinline__ double2 vshfl_xor(unsigned mask, const double2 &v, int lane_mask) {
+    return make_double2(__shfl_xor_sync(mask, v.x, lane_mask), __shfl_xor_sync(mask, v.y, lane_mask));
+}
+__device__ __forceinline__ void vadd(float4 &a, const float4 &b) {
+    a.x += b.x;
+    a.y += b.y;
+    a.z += b.z;
+    a.w += b.w;
+}
+__device__ __forceinline__ void vadd(double2 &a, const double2 &b) {
+    a.x += b.x;
+    a.y += b.y;
+}
+
+// Read-only gather of a dense-operand vector: cached in L1 and L2 (rows are re-used by
+// neighbouring rows of the sparse matrix).
+template <typename V>
+__device__ __forceinline__ V ld_dense(const V *p) {
+    return __ldg(p);
+}
+
+// Streaming read of CSR data (touched once): do not let it displace dense rows in L1.
+__device__ __forceinline__ int ld_stream(const int *p) { return __ldcs(p); }
+__device__ __forceinline__ float ld_stream(const float *p) { return __ldcs(p); }
+__device__ __forceinline__ double ld_stream(const double *p) { return __ldcs(p); }
+
+// Streaming store of results (written once, not read again by this kernel).
+template <typename V>
+__device__ __forceinline__ void st_stream(V *p, const V &v) {
+    __stcs(p, v);
+}
+
+// Lane mask of the L-lane group that `lane` belongs to (L a power of two <= 32).
+template <int L>
+__device__ __forceinline__ unsigned group_mask(int lane) {
+    if constexpr (L == 32) {
+        return 0xffffffffu;
+    } else {
+        return ((1u << L) - 1u) << (lane & ~(L - 1));
+    }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace rode

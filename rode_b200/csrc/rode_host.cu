@@ -1,0 +1,180 @@
+// Host side of librode_b200: status reporting, the per-device workspace cache, and the C++
+// entry points with the reference's own signatures (RoDeSpmm.h, RoDeSddmm.h,
+// RoDePreprocess.h), each a thin wrapper over the C ABI in rode_b200.h.
+#include <cstring>
+#include <mutex>
+
+#include "RoDePreprocess.h"
+#include "RoDeSddmm.h"
+#include "RoDeSpmm.h"
+#include "rode_common.cuh"
+
+namespace rode {
+
+char *error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+int fail(int status, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error_buffer(), 512, fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+namespace {
+
+// One growable scratch buffer per device and purpose, owned by the library for callers of
+// the reference-signature entry points, which carry no workspace argument.  Growing frees
+// the old buffer with cudaFree, which waits for work that may still use it.
+struct DeviceScratch {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+constexpr int kMaxDevices = 64;
+enum ScratchKind { kSpmmScratch = 0, kPreprocessScratch = 1, kScratchKinds = 2 };
+DeviceScratch g_scratch[kScratchKinds][kMaxDevices];
+std::mutex g_scratch_mutex;
+
+int scratch_for(ScratchKind kind, size_t bytes, void **out) {
+    *out = nullptr;
+    if (bytes == 0) return RODE_OK;
+    int dev = 0;
+    RODE_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(RODE_ERR_NO_DEVICE, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    DeviceScratch &s = g_scratch[kind][dev];
+    if (s.bytes < bytes) {
+        if (s.ptr) RODE_CUDA_TRY(cudaFree(s.ptr));
+        s.ptr = nullptr;
+        s.bytes = 0;
+        const size_t grown = bytes + bytes / 4;  // head-room against repeated regrowth
+        RODE_CUDA_TRY(cudaMalloc(&s.ptr, grown));
+        s.bytes = grown;
+    }
+    *out = s.ptr;
+    return RODE_OK;
+}
+
+template <typename T>
+void spmm_entry(int tile, int m1, int m2, int k, int n, const T *values, const int *col, const int *row_offsets,
+                const int *blk, const int *res, const int *st, const T *B, T *C, cudaStream_t s1,
+                cudaStream_t s2) {
+    if (n <= 0 || n % tile != 0) {
+        fail(RODE_ERR_INVALID_ARGUMENT, "RoDeSpmm: n = %d is not a multiple of the %d-wide tile", n, tile);
+        return;
+    }
+    size_t need = 0;
+    if (rode_spmm_workspace_bytes(m1, n, static_cast<int>(sizeof(T)), &need) != RODE_OK) return;
+    void *ws = nullptr;
+    if (scratch_for(kSpmmScratch, need, &ws) != RODE_OK) return;
+    if (sizeof(T) == 4)
+        rode_spmm_f32(m1, m2, k, n, reinterpret_cast<const float *>(values), col, row_offsets, blk, res, st,
+                      reinterpret_cast<const float *>(B), reinterpret_cast<float *>(C), ws, need, s1, s2);
+    else
+        rode_spmm_f64(m1, m2, k, n, reinterpret_cast<const double *>(values), col, row_offsets, blk, res, st,
+                      reinterpret_cast<const double *>(B), reinterpret_cast<double *>(C), ws, need, s1, s2);
+}
+
+}  // namespace
+}  // namespace rode
+
+extern "C" const char *rode_last_error(void) { return rode::error_buffer(); }
+extern "C" const char *rode_version(void) { return "0.1.0"; }
+
+// ---- reference-signature C++ entry points ---------------------------------------------
+
+void RoDeSpmm_n32(int m1, int m2, int k, int n, const float *__restrict__ values,
+                  const int *__restrict__ column_indices, const int *__restrict__ row_offsets,
+                  const int *__restrict__ row_indices1, const int *__restrict__ row_indices2,
+                  const int *__restrict__ row_seg_st_offsets, const float *B, float *C, cudaStream_t stream1,
+                  cudaStream_t stream2) {
+    rode::spmm_entry<float>(32, m1, m2, k, n, values, column_indices, row_offsets, row_indices1, row_indices2,
+                            row_seg_st_offsets, B, C, stream1, stream2);
+}
+
+void RoDeSpmm_n128(int m1, int m2, int k, int n, const float *__restrict__ values,
+                   const int *__restrict__ column_indices, const int *__restrict__ row_offsets,
+                   const int *__restrict__ row_indices1, const int *__restrict__ row_indices2,
+                   const int *__restrict__ row_seg_st_offsets, const float *B, float *C, cudaStream_t stream1,
+                   cudaStream_t stream2) {
+    rode::spmm_entry<float>(64, m1, m2, k, n, values, column_indices, row_offsets, row_indices1, row_indices2,
+                            row_seg_st_offsets, B, C, stream1, stream2);
+}
+
+void RoDeSpmm_n32(int m1, int m2, int k, int n, const double *__restrict__ values,
+                  const int *__restrict__ column_indices, const int *__restrict__ row_offsets,
+                  const int *__restrict__ row_indices1, const int *__restrict__ row_indices2,
+                  const int *__restrict__ row_seg_st_offsets, const double *B, double *C, cudaStream_t stream1,
+                  cudaStream_t stream2) {
+    rode::spmm_entry<double>(32, m1, m2, k, n, values, column_indices, row_offsets, row_indices1, row_indices2,
+                             row_seg_st_offsets, B, C, stream1, stream2);
+}
+
+void RoDeSpmm_n128(int m1, int m2, int k, int n, const double *__restrict__ values,
+                   const int *__restrict__ column_indices, const int *__restrict__ row_offsets,
+                   const int *__restrict__ row_indices1, const int *__restrict__ row_indices2,
+                   const int *__restrict__ row_seg_st_offsets, const double *B, double *C, cudaStream_t stream1,
+                   cudaStream_t stream2) {
+    rode::spmm_entry<double>(64, m1, m2, k, n, values, column_indices, row_offsets, row_indices1, row_indices2,
+                             row_seg_st_offsets, B, C, stream1, stream2);
+}
+
+namespace {
+void sddmm_entry(int expect_k, int m1, int m2, int n, int k, const int *blk, const int *res, const int *st,
+                 const int *row_offsets, const int *col, const float *values, const float *lhs, const float *rhs,
+                 float *out, cudaStream_t s1, cudaStream_t s2) {
+    if (k != expect_k) {
+        rode::fail(RODE_ERR_INVALID_ARGUMENT, "RoDeSDDMM_n%d called with k = %d", expect_k, k);
+        return;
+    }
+    rode_sddmm_f32(m1, m2, n, k, blk, res, st, row_offsets, col, values, lhs, rhs, out, s1, s2);
+}
+}  // namespace
+
+void RoDeSDDMM_n32(int m1, int m2, int n, int k, const int *__restrict__ row_indices_block,
+                   const int *__restrict__ row_indices_residue, const int *__restrict__ st_offsets,
+                   const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
+                   const float *__restrict__ values, const float *__restrict__ lhs_matrix,
+                   const float *__restrict__ rhs_matrix, float *__restrict__ out, cudaStream_t stream1,
+                   cudaStream_t stream2) {
+    sddmm_entry(32, m1, m2, n, k, row_indices_block, row_indices_residue, st_offsets, row_offsets, column_indices,
+                values, lhs_matrix, rhs_matrix, out, stream1, stream2);
+}
+
+void RoDeSDDMM_n64(int m1, int m2, int n, int k, const int *__restrict__ row_indices_block,
+                   const int *__restrict__ row_indices_residue, const int *__restrict__ st_offsets,
+                   const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
+                   const float *__restrict__ values, const float *__restrict__ lhs_matrix,
+                   const float *__restrict__ rhs_matrix, float *__restrict__ out, cudaStream_t stream1,
+                   cudaStream_t stream2) {
+    sddmm_entry(64, m1, m2, n, k, row_indices_block, row_indices_residue, st_offsets, row_offsets, column_indices,
+                values, lhs_matrix, rhs_matrix, out, stream1, stream2);
+}
+
+void RoDeSDDMM_n128(int m1, int m2, int n, int k, const int *__restrict__ row_indices_block,
+                    const int *__restrict__ row_indices_residue, const int *__restrict__ st_offsets,
+                    const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
+                    const float *__restrict__ values, const float *__restrict__ lhs_matrix,
+                    const float *__restrict__ rhs_matrix, float *__restrict__ out, cudaStream_t stream1,
+                    cudaStream_t stream2) {
+    sddmm_entry(128, m1, m2, n, k, row_indices_block, row_indices_residue, st_offsets, row_offsets,
+                column_indices, values, lhs_matrix, rhs_matrix, out, stream1, stream2);
+}
+
+void RoDe_preprocess(int N_SEG, int blockX, int vecLen, int M, const int *row_ptr, int *block_r_ind, int *st_off,
+                     int *residue_r_ind, int *n_blk, int *n_res) {
+    size_t need = 0;
+    if (rode_preprocess_workspace_bytes(M, &need) != RODE_OK) return;
+    void *ws = nullptr;
+    if (rode::scratch_for(rode::kPreprocessScratch, need, &ws) != RODE_OK) return;
+    rode_preprocess(N_SEG, blockX, vecLen, M, row_ptr, block_r_ind, st_off, residue_r_ind, n_blk, n_res, ws, need,
+                    nullptr);
+}
+
+void RoDe_preprocess_cpu(int N_SEG, int blockX, int vecLen, int M, const int *row_ptr, int *block_r_ind,
+                         int *st_off, int *residue_r_ind, int &n_blk, int &n_res) {
+    rode_preprocess_cpu(N_SEG, blockX, vecLen, M, row_ptr, block_r_ind, st_off, residue_r_ind, &n_blk, &n_res);
+}

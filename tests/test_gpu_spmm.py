@@ -1,0 +1,174 @@
+"""SpMM through the C ABI against the CPU oracle (fp64-accumulated ground truth), the
+reference's own kernels where they are built, and size-independent properties."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref
+from rode_b200 import capi
+from rode_b200 import workloads as W
+from tests.helpers import (assert_close_to_truth, gpu_inputs, run_reference_spmm, sample_rows_csr, spmm_abs_scale)
+
+pytestmark = pytest.mark.gpu
+
+
+def _small_families():
+    return {
+        "bernoulli": W.bernoulli(),                                   # config 1 at full size
+        "zipf": W.zipf_rows(m=4096, n=4096, cap=4096, mean=16),       # split rows
+        "stencil": W.stencil27(12),                                   # residue only, m1 == 0
+        "pareto": W.pareto_rows(m=4096, n=8192, cap=3000),
+        "rmat": W.rmat(scale=12),                                     # many empty rows
+    }
+
+
+def _check_against_truth(oracle_cpu, A, B_host, C_dev, what):
+    rp, col, val = A.row_ptr.numpy(), A.col.numpy(), A.val.numpy()
+    truth = oracle_cpu.spmm_f64acc(rp, col, val, B_host, threads=oracle_cpu.max_threads())
+    assert_close_to_truth(C_dev.cpu().numpy(), truth, spmm_abs_scale(rp, col, val, B_host), what)
+
+
+@pytest.mark.parametrize("n", [32, 64, 128])
+def test_spmm_families_against_oracle_and_reference(oracle_cpu, n):
+    for name, A in _small_families().items():
+        d, meta = gpu_inputs(A)
+        B = W.dense(A.n, n, seed=3)
+        Bd = B.cuda()
+        C = capi.spmm(meta, d.row_ptr, d.col, d.val, Bd)
+        torch.cuda.synchronize()
+        _check_against_truth(oracle_cpu, A, B.numpy(), C, f"{name} n={n}")
+        # deterministic: no floating-point atomics
+        C2 = capi.spmm(meta, d.row_ptr, d.col, d.val, Bd)
+        assert torch.equal(C, C2)
+        # the reference's own kernels on the same inputs (needs both kernels to have work)
+        if ref.available() and meta.m1 > 0 and meta.m2 > 0 and n in (32, 128):
+            Cref = run_reference_spmm(d, meta, Bd, n)
+            _check_against_truth(oracle_cpu, A, B.numpy(), Cref, f"reference {name} n={n}")
+            scale = spmm_abs_scale(A.row_ptr.numpy(), A.col.numpy(), A.val.numpy(), B.numpy())
+            assert_close_to_truth(C.cpu().numpy(), Cref.cpu().numpy().astype(np.float64), 2 * scale,
+                                  f"ours vs reference {name} n={n}")
+
+
+@pytest.mark.parametrize("n", [96, 160, 256])
+def test_spmm_other_widths(oracle_cpu, n):
+    A = W.pareto_rows(m=2048, n=3000, cap=1400, seed=9)
+    d, meta = gpu_inputs(A)
+    B = W.dense(A.n, n, seed=4)
+    C = capi.spmm(meta, d.row_ptr, d.col, d.val, B.cuda())
+    _check_against_truth(oracle_cpu, A, B.numpy(), C, f"n={n}")
+
+
+def test_spmm_edge_cases(oracle_cpu):
+    def csr(lens, ncols, seed=0):
+        rng = np.random.default_rng(seed)
+        lens = np.asarray(lens)
+        rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        col = np.concatenate([np.sort(rng.choice(ncols, l, replace=False)) for l in lens] + [np.zeros(0, np.int64)])
+        val = rng.uniform(-1, 1, len(col)).astype(np.float32)
+        return W.CSR(len(lens), ncols, torch.from_numpy(rp), torch.from_numpy(col.astype(np.int32)),
+                     torch.from_numpy(val))
+
+    cases = {
+        "empty rows only": csr([0] * 37, 64),
+        "single long row": csr([20000], 30000),
+        "unaligned long rows": csr([3, 16384, 1, 1025, 2, 513, 0, 0, 545], 20000),
+        "block only (m2 == 0)": csr([32, 64, 512, 1024, 96], 4096),
+        "exact segment edges": csr([511, 512, 513, 1, 543, 544, 545, 31, 32, 33, 0, 1023, 1024, 1025], 2048),
+        "one entry": csr([1], 8),
+    }
+    for name, A in cases.items():
+        d, meta = gpu_inputs(A)
+        if name.startswith("block only"):
+            assert meta.m2 == 0 and meta.m1 > 0
+        for n in (32, 128):
+            B = W.dense(A.n, n, seed=6)
+            # rows named by the metadata are written, not accumulated: start from garbage there
+            C0 = torch.zeros((A.m, n), device="cuda")
+            listed = torch.cat([meta.block_r_ind[: meta.m1], meta.residue_r_ind[: meta.m2]]).long()
+            C0[listed] = float("nan")
+            C = capi.spmm(meta, d.row_ptr, d.col, d.val, B.cuda(), C=C0)
+            _check_against_truth(oracle_cpu, A, B.numpy(), C, f"{name} n={n}")
+    # M == 0: nothing to launch
+    empty = W.CSR(0, 8, torch.zeros(1, dtype=torch.int32), torch.zeros(0, dtype=torch.int32), torch.zeros(0))
+    d, meta = gpu_inputs(empty)
+    assert (meta.m1, meta.m2) == (0, 0)
+    assert capi.spmm(meta, d.row_ptr, d.col, d.val, torch.zeros((8, 32), device="cuda")).shape == (0, 32)
+
+
+def test_spmm_fp64(oracle_cpu):
+    A = W.zipf_rows(m=2048, n=2048, cap=2048)
+    d, meta = gpu_inputs(A)
+    for n in (32, 128, 48):
+        B = W.dense(A.n, n, seed=8, dtype=torch.float64)
+        C = capi.spmm(meta, d.row_ptr, d.col, d.val.double(), B.cuda())
+        truth = oracle_cpu.spmm_f64(A.row_ptr.numpy(), A.col.numpy(), A.val.numpy().astype(np.float64), B.numpy())
+        assert np.allclose(C.cpu().numpy(), truth, rtol=1e-12, atol=1e-12)
+    # the reference's double kernels need double values: run them explicitly
+    if ref.available():
+        B = W.dense(A.n, 32, seed=8, dtype=torch.float64).cuda()
+        dd = W.CSR(d.m, d.n, d.row_ptr, d.col, d.val.double())
+        Cref = run_reference_spmm(dd, meta, B, 32)
+        C = capi.spmm(meta, d.row_ptr, d.col, dd.val, B)
+        assert torch.allclose(C, Cref, rtol=1e-11, atol=1e-11)
+
+
+def test_reference_signature_entry_points(oracle_cpu):
+    """RoDeSpmm_n32 / RoDeSpmm_n128 with the reference's argument order, library-owned workspace."""
+    lib = capi.load()
+    A = W.zipf_rows(m=4096, n=4096, cap=4096)
+    d, meta = gpu_inputs(A)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    vp = ctypes.c_void_p
+    for name, n in (("RoDeSpmm_n32_f32", 32), ("RoDeSpmm_n128_f32", 128), ("RoDeSpmm_n32_f32", 96)):
+        fn = getattr(lib, capi.CPP_SYMBOLS[name])
+        fn.restype = None
+        B = W.dense(A.n, n, seed=2)
+        Bd = B.cuda()
+        C = torch.zeros((A.m, n), device="cuda")
+        torch.cuda.synchronize()
+        fn(meta.m1, meta.m2, A.n, n, vp(d.val.data_ptr()), vp(d.col.data_ptr()), vp(d.row_ptr.data_ptr()),
+           vp(meta.block_r_ind.data_ptr()), vp(meta.residue_r_ind.data_ptr()), vp(meta.st_off.data_ptr()),
+           vp(Bd.data_ptr()), vp(C.data_ptr()), vp(s1.cuda_stream), vp(s2.cuda_stream))
+        s1.synchronize()
+        s2.synchronize()
+        _check_against_truth(oracle_cpu, A, B.numpy(), C, name)
+
+
+def test_spmm_full_size_heavy_tail_config(oracle_cpu):
+    """Config 2 at full size (65536 x 65536 Zipf rows, N = 128): every element checked."""
+    A = W.zipf_rows(device="cuda")
+    meta = capi.preprocess(A.row_ptr, A.nnz)
+    B = W.dense(A.n, 128, device="cuda", seed=3)
+    C = capi.spmm(meta, A.row_ptr, A.col, A.val, B)
+    h = A.to("cpu")
+    _check_against_truth(oracle_cpu, h, B.cpu().numpy(), C, "config 2")
+
+
+@pytest.mark.parametrize("family,n", [("stencil", 64), ("pareto", 128), ("rmat", 128)])
+def test_spmm_full_size_properties(oracle_cpu, family, n):
+    """Full-size matrices: linearity in B, and exact agreement with the oracle on a sample of
+    rows (longest rows, empty rows and a random draw)."""
+    A = {"stencil": lambda: W.stencil27(128, device="cuda"),
+         "pareto": lambda: W.pareto_rows(device="cuda"),
+         "rmat": lambda: W.rmat(scale=22, device="cuda")}[family]()
+    meta = capi.preprocess(A.row_ptr, A.nnz)
+    B1 = W.dense(A.n, n, device="cuda", seed=3)
+    C1 = capi.spmm(meta, A.row_ptr, A.col, A.val, B1)
+    # sample of rows against the oracle
+    lens = (A.row_ptr[1:] - A.row_ptr[:-1]).long()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rows = torch.cat([torch.topk(lens, 16).indices, torch.nonzero(lens == 0).flatten()[:64],
+                      torch.randint(0, A.m, (4096,), device="cuda", generator=g)]).unique()
+    rp, col, val, _ = sample_rows_csr(A, rows)
+    Bh = B1.cpu().numpy()
+    truth = oracle_cpu.spmm_f64acc(rp, col, val, Bh, threads=oracle_cpu.max_threads())
+    assert_close_to_truth(C1[rows].cpu().numpy(), truth, spmm_abs_scale(rp, col, val, Bh), f"{family} sample")
+    # linearity: S(2 B1 - B2) == 2 S B1 - S B2 up to rounding of the combination
+    B2 = W.dense(A.n, n, device="cuda", seed=4)
+    C2 = capi.spmm(meta, A.row_ptr, A.col, A.val, B2)
+    C3 = capi.spmm(meta, A.row_ptr, A.col, A.val, 2 * B1 - B2)
+    resid = (C3 - (2 * C1 - C2)).abs().max().item()
+    assert resid <= 1e-3 * max(1.0, C1.abs().max().item()), resid
+    del C2, C3
