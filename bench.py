@@ -1,0 +1,565 @@
+#!/usr/bin/env python
+"""Benchmark of the RoDe hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload: SpMM, N = 128, fp32, on an R-MAT scale-23 graph (8,388,608 vertices,
+edge factor 16, a/b/c/d = 0.57/0.19/0.19/0.05, duplicates removed), rows nnz-balanced over
+the ranks, dense operand broadcast once at set-up.  One "step" is one pass of the hot path
+(block, fix-up and residue kernels) over the rank's rows.  `value` is whole-job
+GFLOP/s = 2 * nnz * N / (max over ranks of the device time per step).
+
+The same line carries: `roofline` (dominant kernel, algorithmic bytes / measured time
+against the measured HBM copy bandwidth), `e2e` (host buffers -> H2D -> preprocessing ->
+SpMM -> D2H every step), `sddmm` (K = 64 on the same matrix), `cpu_baseline` (CPU oracle on
+the host cores, N = 1 only) and, at N = 1, `configs`: the other benchmark matrices with the
+reference's own kernels (compiled for sm_100a into oracle/_ref) timed beside ours.
+
+`--impl reference` times the CPU implementation (the oracle's restatement of CSR SpMM; the
+reference has no CPU SpMM of its own) on all host threads and prints the same line shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+N_DENSE = 128
+K_SDDMM = 64
+METRIC = "SpMM GFLOP/s (2*nnz*N), fp32"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--scale", type=int, default=23, help="R-MAT scale of the headline workload")
+    p.add_argument("--no-extra", action="store_true", help="skip the secondary configs and the CPU baseline")
+    p.add_argument("--e2e-steps", type=int, default=3)
+    return p.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ---------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clock/throttle samples while the timed region runs (read-only query)."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = f"/tmp/rode_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, f[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------
+def spmm_bmin(nnz, m, n_dense, k_touched):
+    return 8 * nnz + 4 * (m + 1) + 4 * n_dense * k_touched + 4 * n_dense * m
+
+
+def sddmm_bmin(nnz, m, k, m_nonempty, k_touched):
+    return 12 * nnz + 4 * (m + 1) + 4 * k * m_nonempty + 4 * k * k_touched
+
+
+def distinct_count(t: torch.Tensor) -> int:
+    if t.numel() == 0:
+        return 0
+    s, _ = torch.sort(t)
+    return int((s[1:] != s[:-1]).sum()) + 1
+
+
+def time_loop(fn, steps, warmup, stream, flush=None):
+    """Average device milliseconds per call of fn over `steps` calls (after `warmup`), with
+    CUDA events on `stream`.  With `flush`, a buffer larger than L2 is rewritten before each
+    call and every call is timed by its own event pair (median reported)."""
+    for _ in range(warmup):
+        if flush is not None:
+            flush.add_(1.0)
+        fn()
+    torch.cuda.synchronize()
+    if flush is None:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(steps):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+    times = []
+    for _ in range(steps):
+        flush.add_(1.0)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+class ForkJoin:
+    """Runs the two-stream entry points so that one timing stream sees all of the work:
+    block work on the current stream, residue work on a side stream forked from and joined
+    back into it."""
+
+    def __init__(self, device):
+        self.cur = torch.cuda.current_stream(device)
+        self.side = torch.cuda.Stream(device)
+        self.fork = torch.cuda.Event()
+        self.join = torch.cuda.Event()
+
+    def run(self, launch):
+        self.fork.record(self.cur)
+        self.side.wait_event(self.fork)
+        launch(self.cur, self.side)
+        self.join.record(self.side)
+        self.cur.wait_event(self.join)
+
+
+# ---------------------------------------------------------------------------------------
+def reference_arm(args, rank, world):
+    """CPU implementation on the host cores: the oracle's CSR SpMM (the reference ships no
+    CPU SpMM), all threads, on a bounded sample of the headline workload."""
+    if rank != 0:
+        return
+    from oracle import cpu
+    from rode_b200 import workloads as W
+
+    threads = cpu.max_threads()
+    scale = min(args.scale, 20)  # bounded sample: same generator and width, 2^20 vertices
+    A = W.rmat(scale=scale, device="cpu")
+    B = W.dense(A.n, N_DENSE, seed=3).numpy()
+    rp, col, val = A.row_ptr.numpy(), A.col.numpy(), A.val.numpy()
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu.spmm_f32(rp, col, val, B, threads=threads)
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu.spmm_f32(rp, col, val, B, threads=threads)
+    ms = (time.perf_counter() - t0) / steps * 1e3
+    gflops = 2.0 * A.nnz * N_DENSE / (ms * 1e-3) / 1e9
+    sample = f"R-MAT scale {scale} (nnz {A.nnz}), N={N_DENSE}, full pass per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gflops, "unit": "GFLOP/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"rmat{args.scale}_spmm_n{N_DENSE}", "sample": sample},
+        "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": gflops, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------
+def secondary_configs(peak_gbs, steps, warmup):
+    """The other benchmark matrices at N = 1: ours and, where its preconditions hold, the
+    reference's own kernels compiled for sm_100a (oracle/_ref), on the same device arrays."""
+    from oracle import ref
+    from rode_b200 import capi
+    from rode_b200 import workloads as W
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    fj = ForkJoin(dev)
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)  # 256 MB > L2
+    out = {}
+    have_ref = ref.available()
+    specs = [
+        ("cfg1_bernoulli4096", lambda: W.bernoulli(device=dev), [("spmm", 32), ("sddmm", 32)]),
+        ("cfg2_zipf65536", lambda: W.zipf_rows(device=dev), [("spmm", 128)]),
+        ("cfg3_stencil128", lambda: W.stencil27(128, device=dev), [("spmm", 64), ("sddmm", 64)]),
+        ("cfg4_pareto1m", lambda: W.pareto_rows(device=dev), [("spmm", 32), ("spmm", 128), ("sddmm", 32),
+                                                              ("sddmm", 128)]),
+    ]
+    for name, make, ops in specs:
+        A = make()
+        k_touched = distinct_count(A.col)
+        lens = A.row_ptr[1:] - A.row_ptr[:-1]
+        m_nonempty = int((lens > 0).sum())
+        for op, width in ops:
+            seg = 32 if (op == "sddmm" and width == 128) else 512
+            meta = capi.preprocess(A.row_ptr, A.nnz, seg, 32, 4)
+            entry = {"nnz": A.nnz, "m1": meta.m1, "m2": meta.m2}
+            if op == "spmm":
+                B = W.dense(A.n, width, device=dev, seed=3)
+                C = torch.zeros((A.m, width), device=dev)
+                need = capi.spmm_workspace_bytes(meta.m1, width, 4)
+                ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+
+                def ours(s1, s2):
+                    capi.spmm_raw(torch.float32, meta.m1, meta.m2, A.n, width, A.val.data_ptr(), A.col.data_ptr(),
+                                  A.row_ptr.data_ptr(), meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(),
+                                  meta.st_off.data_ptr(), B.data_ptr(), C.data_ptr(), ws.data_ptr(), need, s1, s2)
+
+                def theirs(s1, s2):
+                    ref.spmm_gpu(32 if width == 32 else 128, False, meta.m1, meta.m2, A.n, width, A.val.data_ptr(),
+                                 A.col.data_ptr(), A.row_ptr.data_ptr(), meta.block_r_ind.data_ptr(),
+                                 meta.residue_r_ind.data_ptr(), meta.st_off.data_ptr(), B.data_ptr(), C.data_ptr(),
+                                 s1.cuda_stream, s2.cuda_stream)
+
+                bmin = spmm_bmin(A.nnz, A.m, width, k_touched)
+                # the reference's kernels: both grids non-empty, width 32 or a multiple of 64,
+                # and byte offsets col * n * 4 below 2^31
+                ref_ok = (have_ref and meta.m1 > 0 and meta.m2 > 0 and width in (32, 128)
+                          and (A.n - 1) * width * 4 < 2**31)
+            else:
+                lhs = W.dense(A.m, width, device=dev, seed=5)
+                rhs = W.dense(A.n, width, device=dev, seed=6)
+                res = torch.zeros(A.nnz, device=dev)
+
+                def ours(s1, s2):
+                    capi.sddmm_raw(meta.m1, meta.m2, A.n, width, meta.block_r_ind.data_ptr(),
+                                   meta.residue_r_ind.data_ptr(), meta.st_off.data_ptr(), A.row_ptr.data_ptr(),
+                                   A.col.data_ptr(), A.val.data_ptr(), lhs.data_ptr(), rhs.data_ptr(), res.data_ptr(),
+                                   s1, s2)
+
+                def theirs(s1, s2):
+                    ref.sddmm_gpu(width, meta.m1, meta.m2, A.n, meta.block_r_ind.data_ptr(),
+                                  meta.residue_r_ind.data_ptr(), meta.st_off.data_ptr(), A.row_ptr.data_ptr(),
+                                  A.col.data_ptr(), A.val.data_ptr(), lhs.data_ptr(), rhs.data_ptr(), res.data_ptr(),
+                                  s1.cuda_stream, s2.cuda_stream)
+
+                bmin = sddmm_bmin(A.nnz, A.m, width, m_nonempty, k_touched)
+                # the reference SDDMM skips a kernel on a null stream and has K = 32 / 128 only
+                ref_ok = have_ref and width in (32, 128) and meta.m1 > 0 and meta.m2 > 0 and (A.n - 1) * width < 2**29
+            ms = time_loop(lambda: fj.run(ours), steps, warmup, fj.cur, flush)
+            entry.update({"ms": ms, "gflops": 2.0 * A.nnz * width / ms / 1e6, "bmin_bytes": bmin,
+                          "algorithmic_gbs": bmin / ms / 1e6, "frac_of_measured_hbm": bmin / ms / 1e6 / peak_gbs})
+            if ref_ok:
+                side1 = torch.cuda.Stream(dev)  # the reference needs two real (non-null) streams
+
+                def run_theirs():
+                    fj.fork.record(fj.cur)
+                    side1.wait_event(fj.fork)
+                    fj.side.wait_event(fj.fork)
+                    theirs(side1, fj.side)
+                    e1, e2 = torch.cuda.Event(), torch.cuda.Event()
+                    e1.record(side1)
+                    e2.record(fj.side)
+                    fj.cur.wait_event(e1)
+                    fj.cur.wait_event(e2)
+
+                rms = time_loop(run_theirs, steps, warmup, fj.cur, flush)
+                entry.update({"reference_kernels_ms": rms, "speedup_vs_reference_kernels": rms / ms})
+            out[f"{name}_{op}{width}"] = entry
+            torch.cuda.synchronize()
+        del A
+        torch.cuda.empty_cache()
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+        return
+
+    import torch.distributed as dist
+
+    from rode_b200 import capi
+    from rode_b200 import workloads as W
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path")
+    capi.load()  # fails loudly when librode_b200.so is missing
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def sum_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t)
+
+    peak_gbs, peak_kind = measured_peak()
+
+    # ---- set-up: rank 0 draws the matrix and the dense operands; one broadcast each -------
+    t_setup = time.perf_counter()
+    n_vert = 1 << args.scale
+    if rank == 0:
+        A = W.rmat(scale=args.scale, device=dev)
+        sizes = torch.tensor([A.nnz], dtype=torch.int64, device=dev)
+    else:
+        A = None
+        sizes = torch.zeros(1, dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.broadcast(sizes, 0)
+    nnz = int(sizes[0])
+    if rank == 0:
+        row_ptr, col, val = A.row_ptr, A.col, A.val
+        X = W.dense(n_vert, N_DENSE, device=dev, seed=3)
+        rhs = W.dense(n_vert, K_SDDMM, device=dev, seed=6)
+    else:
+        row_ptr = torch.empty(n_vert + 1, dtype=torch.int32, device=dev)
+        col = torch.empty(nnz, dtype=torch.int32, device=dev)
+        val = torch.empty(nnz, dtype=torch.float32, device=dev)
+        X = torch.empty((n_vert, N_DENSE), dtype=torch.float32, device=dev)
+        rhs = torch.empty((n_vert, K_SDDMM), dtype=torch.float32, device=dev)
+    broadcast_ms = None
+    if world > 1:
+        for t in (row_ptr, col, val, rhs):
+            dist.broadcast(t, 0)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.broadcast(X, 0)  # the dense operand of the headline op: one NCCL broadcast
+        e1.record()
+        torch.cuda.synchronize()
+        broadcast_ms = e0.elapsed_time(e1)
+    full = W.CSR(n_vert, n_vert, row_ptr, col, val)
+    bounds = W.partition_rows(row_ptr, world)
+    r0, r1 = bounds[rank], bounds[rank + 1]
+    mine = full.rows(r0, r1)
+    if world > 1:
+        del full, row_ptr, col, val
+        torch.cuda.empty_cache()
+    my_nnz, my_rows = mine.nnz, mine.m
+    meta = capi.preprocess(mine.row_ptr, my_nnz, 512, 32, 4)
+    C = torch.zeros((my_rows, N_DENSE), dtype=torch.float32, device=dev)
+    ws_bytes = capi.spmm_workspace_bytes(meta.m1, N_DENSE, 4)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    fj = ForkJoin(dev)
+    setup_s = time.perf_counter() - t_setup
+
+    def spmm_launch(s1, s2, m1=None, m2=None):
+        capi.spmm_raw(torch.float32, meta.m1 if m1 is None else m1, meta.m2 if m2 is None else m2, n_vert, N_DENSE,
+                      mine.val.data_ptr(), mine.col.data_ptr(), mine.row_ptr.data_ptr(), meta.block_r_ind.data_ptr(),
+                      meta.residue_r_ind.data_ptr(), meta.st_off.data_ptr(), X.data_ptr(), C.data_ptr(),
+                      ws.data_ptr(), ws_bytes, s1, s2)
+
+    def step():
+        fj.run(spmm_launch)
+
+    # ---- timed region -------------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(fj.cur)
+    for _ in range(args.steps):
+        step()
+    b.record(fj.cur)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = max_over_ranks(a.elapsed_time(b) / args.steps)
+    launches_per_step = (2 if meta.m1 > 0 else 0) + (1 if meta.m2 > 0 else 0)
+    gflops = 2.0 * nnz * N_DENSE / ms_step / 1e6
+
+    # ---- per-kernel timing and the roofline of the dominant kernel ---------------------------
+    lens = (mine.row_ptr[1:] - mine.row_ptr[:-1]).to(torch.int64)
+    aligned = lens + (mine.row_ptr[:-1] % 4)
+    in_block = aligned >= 32                                   # rows finished by spmm_block
+    rows_block = int(in_block.sum())
+    nnz_block = int(lens[in_block].sum())
+    entry_in_block = torch.repeat_interleave(in_block, lens)
+    kt_block = distinct_count(mine.col[entry_in_block])
+    kt_all = distinct_count(mine.col)
+    del entry_in_block
+    block_bytes = 8 * nnz_block + 4 * N_DENSE * kt_block + 4 * N_DENSE * rows_block
+    ms_block = time_loop(lambda: spmm_launch(fj.cur, fj.cur, m2=0), args.steps, 3, fj.cur) if meta.m1 > 0 else 0.0
+    ms_residue = time_loop(lambda: spmm_launch(fj.cur, fj.cur, m1=0), args.steps, 3, fj.cur) if meta.m2 > 0 else 0.0
+    ms_block = max_over_ranks(ms_block)
+    ms_residue = max_over_ranks(ms_residue)
+    block_bytes_all = sum_over_ranks(float(block_bytes))
+    step_bytes_all = sum_over_ranks(float(spmm_bmin(my_nnz, my_rows, N_DENSE, kt_all)))
+    roofline = {
+        "kernel": "rode::spmm_block<float,32> (+ spmm_fixup on the same stream)",
+        "bound": "hbm", "achieved": block_bytes_all / world / ms_block / 1e6 if ms_block else None,
+        "peak": peak_gbs, "unit": "GB/s", "peak_kind": f"of {peak_kind}",
+        "frac": (block_bytes_all / world / ms_block / 1e6 / peak_gbs) if ms_block else None,
+        "traffic": None, "algorithmic_bytes_per_launch": block_bytes_all / world, "ms_per_launch": ms_block,
+        "residue_kernel_ms": ms_residue,
+        "step": {"algorithmic_bytes": step_bytes_all, "achieved": step_bytes_all / ms_step / 1e6,
+                 "frac": step_bytes_all / ms_step / 1e6 / (peak_gbs * world)},
+    }
+    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_path):
+        try:
+            roofline["traffic"] = json.load(open(traffic_path)).get("spmm_block_rmat23_n128_bytes_per_launch")
+        except Exception:
+            pass
+
+    # ---- SDDMM K = 64 on the same rows ---------------------------------------------------------
+    lhs = W.dense(n_vert, K_SDDMM, device=dev, seed=5)[r0:r1].contiguous()
+    out = torch.zeros(my_nnz, dtype=torch.float32, device=dev)
+
+    def sddmm_launch(s1, s2):
+        capi.sddmm_raw(meta.m1, meta.m2, n_vert, K_SDDMM, meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(),
+                       meta.st_off.data_ptr(), mine.row_ptr.data_ptr(), mine.col.data_ptr(), mine.val.data_ptr(),
+                       lhs.data_ptr(), rhs.data_ptr(), out.data_ptr(), s1, s2)
+
+    barrier()
+    ms_sddmm = max_over_ranks(time_loop(lambda: fj.run(sddmm_launch), args.steps, 3, fj.cur))
+    sddmm_bytes = sum_over_ranks(float(sddmm_bmin(my_nnz, my_rows, K_SDDMM, int((lens > 0).sum()), kt_all)))
+    sddmm = {"metric": "SDDMM GFLOP/s (2*nnz*K), fp32", "k": K_SDDMM, "ms_per_step": ms_sddmm,
+             "value": 2.0 * nnz * K_SDDMM / ms_sddmm / 1e6, "unit": "GFLOP/s", "algorithmic_bytes": sddmm_bytes,
+             "algorithmic_gbs": sddmm_bytes / ms_sddmm / 1e6,
+             "frac_of_measured_hbm": sddmm_bytes / ms_sddmm / 1e6 / (peak_gbs * world)}
+    del lhs, out
+
+    # ---- end to end: host buffers in, host result out, every step -----------------------------
+    h_rp, h_col, h_val = (t.cpu().pin_memory() for t in (mine.row_ptr, mine.col, mine.val))
+    h_X = X.cpu().pin_memory()
+    h_C = torch.empty((my_rows, N_DENSE), dtype=torch.float32).pin_memory()
+    d_rp, d_col, d_val, d_X = (torch.empty_like(t) for t in (mine.row_ptr, mine.col, mine.val, X))
+    h2d = sum(t.numel() * t.element_size() for t in (h_rp, h_col, h_val, h_X))
+    d2h = h_C.numel() * 4
+
+    def e2e_step():
+        d_rp.copy_(h_rp, non_blocking=True)
+        d_col.copy_(h_col, non_blocking=True)
+        d_val.copy_(h_val, non_blocking=True)
+        d_X.copy_(h_X, non_blocking=True)
+        m = capi.preprocess(d_rp, my_nnz, 512, 32, 4)   # device-side row decomposition (reads 2 counts back)
+        C.zero_()                                        # the API's contract: C arrives zero-filled
+
+        def launch(s1, s2):
+            capi.spmm_raw(torch.float32, m.m1, m.m2, n_vert, N_DENSE, d_val.data_ptr(), d_col.data_ptr(),
+                          d_rp.data_ptr(), m.block_r_ind.data_ptr(), m.residue_r_ind.data_ptr(), m.st_off.data_ptr(),
+                          d_X.data_ptr(), C.data_ptr(), ws.data_ptr(), ws_bytes, s1, s2)
+
+        fj.run(launch)
+        h_C.copy_(C, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    a.record(fj.cur)
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    b.record(fj.cur)
+    barrier()
+    ms_e2e = max_over_ranks(a.elapsed_time(b) / args.e2e_steps)
+    e2e = {"value": 2.0 * nnz * N_DENSE / ms_e2e / 1e6, "unit": "GFLOP/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
+           "includes": "H2D of CSR + dense operand from pinned memory, device preprocessing, C zero-fill, SpMM, D2H of C"}
+    checksum = float(h_C.double().sum())
+
+    # ---- CPU baseline (rank 0, single-GPU run only) ----------------------------------------------
+    cpu_baseline = None
+    configs = None
+    if world == 1 and not args.no_extra:
+        from oracle import cpu
+
+        threads = cpu.max_threads()
+        rows_sample = min(my_rows, 1 << 20)             # first 2^20 rows of the same matrix, full width
+        rp_s = h_rp[: rows_sample + 1].numpy()
+        nnz_s = int(rp_s[-1])
+        t0 = time.perf_counter()
+        cpu.spmm_f32(rp_s, h_col.numpy()[:nnz_s], h_val.numpy()[:nnz_s], h_X.numpy(), threads=threads)
+        dt = time.perf_counter() - t0
+        cpu_baseline = {"value": 2.0 * nnz_s * N_DENSE / dt / 1e9, "unit": "GFLOP/s", "cores": threads, "kind": "port",
+                        "sample": f"rows 0..{rows_sample} of the headline matrix (nnz {nnz_s}), one pass, {dt:.2f} s",
+                        "note": "the reference has no CPU SpMM; this is the oracle's CSR SpMM with OpenMP over rows"}
+        del h_rp, h_col, h_val, h_X, h_C, d_rp, d_col, d_val, d_X
+        torch.cuda.empty_cache()
+        configs = secondary_configs(peak_gbs, min(args.steps, 10), 3)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": gflops, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"rmat{args.scale}_spmm_n{N_DENSE}", "rows": n_vert, "nnz": nnz, "n": N_DENSE,
+                       "partition": f"nnz-balanced contiguous rows over {world} rank(s)",
+                       "l2": "inputs larger than L2 (dense operand 4.3 GB, CSR 1 GB); no flush between steps",
+                       "m1_rank0": meta.m1, "m2_rank0": meta.m2},
+            "clocks": clocks, "gpu_launches": launches_per_step * args.steps, "nnz_per_s": nnz / ms_step * 1e3,
+            "roofline": roofline, "e2e": e2e, "sddmm": sddmm, "cpu_baseline": cpu_baseline,
+            "broadcast_ms": broadcast_ms, "setup_s": setup_s, "checksum": checksum,
+        }
+        if configs is not None:
+            line["configs"] = configs
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
