@@ -49,6 +49,11 @@ def parse_args():
     p.add_argument("--scale", type=int, default=23, help="R-MAT scale of the headline workload")
     p.add_argument("--no-extra", action="store_true", help="skip the secondary configs and the CPU baseline")
     p.add_argument("--e2e-steps", type=int, default=3)
+    p.add_argument("--only", choices=["spmm", "sddmm"], default=None,
+                   help="small single-op run (one family, one width) for profiling and A/B timing")
+    p.add_argument("--family", default="rmat", choices=["bernoulli", "zipf", "stencil", "pareto", "rmat"])
+    p.add_argument("--width", type=int, default=128, help="N of SpMM / K of SDDMM for --only")
+    p.add_argument("--size", type=float, default=1.0, help="row-count factor of the family for --only")
     return p.parse_args()
 
 
@@ -312,6 +317,70 @@ def secondary_configs(peak_gbs, steps, warmup):
     return out
 
 
+def make_family(name, device, scale=23, size=1.0):
+    from rode_b200 import workloads as W
+
+    if name == "bernoulli":
+        return W.bernoulli(device=device)
+    if name == "zipf":
+        m = int(65536 * size)
+        return W.zipf_rows(m=m, n=m, device=device)
+    if name == "stencil":
+        return W.stencil27(max(4, int(round(128 * size ** (1.0 / 3.0)))), device=device)
+    if name == "pareto":
+        m = int((1 << 20) * size)
+        return W.pareto_rows(m=m, n=m, device=device)
+    return W.rmat(scale=scale, device=device)
+
+
+def single_op(args):
+    """One family, one op, one width on cuda:0: `warmup` untimed and `steps` timed launches of
+    the entry point and nothing else (the run the ncu summaries under profiles/ come from)."""
+    from rode_b200 import capi
+    from rode_b200 import workloads as W
+
+    capi.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak_gbs, peak_kind = measured_peak()
+    A = make_family(args.family, dev, args.scale, args.size)
+    width = args.width
+    seg = 32 if (args.only == "sddmm" and width == 128) else 512
+    meta = capi.preprocess(A.row_ptr, A.nnz, seg, 32, 4)
+    fj = ForkJoin(dev)
+    k_touched = distinct_count(A.col)
+    lens = A.row_ptr[1:] - A.row_ptr[:-1]
+    if args.only == "spmm":
+        B = W.dense(A.n, width, device=dev, seed=3)
+        C = torch.zeros((A.m, width), device=dev)
+        need = capi.spmm_workspace_bytes(meta.m1, width, 4)
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+
+        def launch(s1, s2):
+            capi.spmm_raw(torch.float32, meta.m1, meta.m2, A.n, width, A.val.data_ptr(), A.col.data_ptr(),
+                          A.row_ptr.data_ptr(), meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(),
+                          meta.st_off.data_ptr(), B.data_ptr(), C.data_ptr(), ws.data_ptr(), need, s1, s2)
+
+        bmin = spmm_bmin(A.nnz, A.m, width, k_touched)
+    else:
+        lhs = W.dense(A.m, width, device=dev, seed=5)
+        rhs = W.dense(A.n, width, device=dev, seed=6)
+        res = torch.zeros(A.nnz, device=dev)
+
+        def launch(s1, s2):
+            capi.sddmm_raw(meta.m1, meta.m2, A.n, width, meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(),
+                           meta.st_off.data_ptr(), A.row_ptr.data_ptr(), A.col.data_ptr(), A.val.data_ptr(),
+                           lhs.data_ptr(), rhs.data_ptr(), res.data_ptr(), s1, s2)
+
+        bmin = sddmm_bmin(A.nnz, A.m, width, int((lens > 0).sum()), k_touched)
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    ms = time_loop(lambda: fj.run(launch), args.steps, args.warmup, fj.cur, flush)
+    print(json.dumps({"only": args.only, "family": args.family, "width": width, "rows": A.m, "nnz": A.nnz,
+                      "m1": meta.m1, "m2": meta.m2, "ms": ms, "gflops": 2.0 * A.nnz * width / ms / 1e6,
+                      "bmin_bytes": bmin, "algorithmic_gbs": bmin / ms / 1e6,
+                      "frac": bmin / ms / 1e6 / peak_gbs, "peak_kind": peak_kind, "k_touched": k_touched}))
+
+
 # ---------------------------------------------------------------------------------------
 def main():
     args = parse_args()
@@ -320,6 +389,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         reference_arm(args, rank, world)
+        return
+    if args.only is not None:
+        single_op(args)
         return
 
     import torch.distributed as dist
