@@ -2,25 +2,36 @@
 //
 // Stands in for the reference's block / residue kernels (RoDe_SpMM/RoDeSpmm.cu:197-476 and
 // :41-195) and their launcher (:492-529).  The work split follows the reference's metadata
-// (one unit per block segment, one per residue row); what each unit does is new:
+// (block segments, residue rows); how the work is done is new:
 //
-//  * A dense row of the tile is covered by L lanes, 16 bytes per lane (one LDG.128), so a
-//    gather of B[col, tile] is one fully coalesced request of 16*L bytes.  L = 8, 16 or 32;
-//    a warp holds G = 32/L such lane groups.
-//  * spmm_block: one WARP per block segment.  The warp streams the segment's (col, value)
-//    pairs 32 at a time (coalesced, prefetched one chunk ahead), group g takes entries
-//    g*L .. g*L+L-1 of the chunk, fetches kUnroll dense rows at once per lane and
-//    accumulates in registers.  Groups are combined with log2(G) shuffle steps.
-//    The LAST segment of a row also consumes the row's tail (the part shorter than 32 that
-//    the reference leaves to its residue kernel), so a row that fits one segment is
-//    finished by a single warp and stored with plain vector stores.
+//  * A dense-row slice of the column tile is covered by L lanes, 16 bytes per lane (one
+//    LDG.128), so a gather of B[col, tile] is one coalesced request of 16*L bytes.
+//    L = 8, 16 or 32; a warp holds G = 32/L such lane groups.
+//  * Gathers are issued in batches of U = 8 independent LDG.128 per lane; the (column,
+//    value) pairs of a chunk of 32 nonzeros are fetched two chunks ahead and handed to the
+//    lanes by shuffles.  Bytes in flight per SM = resident warps x 32 x U x 16 B, so the
+//    kernels are kept at 64 registers (32 one-warp CTAs per SM, ~131 KB in flight).  Two
+//    register buffers per lane (software pipelining) were measured and rejected: 168
+//    registers cut the resident warps to 12 and the time went up by 30 %.
+//  * spmm_block: one warp per block segment; the G groups take alternate nonzeros and are
+//    combined with log2(G) shuffle steps at the end.  The LAST segment of a row also
+//    consumes the row's tail (the part shorter than 32 that the reference leaves to its
+//    residue kernel), so a row that fits one segment is finished by a single warp and
+//    stored with plain vector stores.
 //  * Rows cut into several segments: every segment writes its partial row to a workspace
 //    slot (slot = segment index); spmm_fixup, ordered after spmm_block on the same stream,
-//    sums the slots of each such row in segment order (fp64 accumulation) and stores the
+//    sums the slots of each such row in a fixed order (fp64 accumulation) and stores the
 //    row.  No floating-point atomics anywhere: results are deterministic.
-//  * spmm_residue: one L-lane group per residue row that has NO block part (aligned length
-//    < 32); rows with a block part were already finished by spmm_block.  Empty rows in the
-//    list are stored as zeros, as the reference does (RoDeSpmm.cu:185-194).
+//  * spmm_rows (L = 32): residue rows that have no block part (aligned length < 32).  A warp
+//    takes 32 consecutive residue rows at once: lane j reads the descriptor of row j, so the
+//    dependent chain row index -> row pointer -> column -> dense row is paid once per 32
+//    rows, not per row.  The nonzeros of the 32 rows form one entry stream that runs through
+//    the same batched gather; a row is stored when the stream passes its end.
+//    spmm_rows_simple (L = 8, 16): one lane group per residue row.
+//    Empty rows in the list are stored as zeros, as the reference does
+//    (RoDeSpmm.cu:185-194); rows with a block part are skipped (spmm_block finished them).
+//  * CTAs are one warp (block, rows) or two (rows_simple): a CTA's slot is held until its
+//    slowest warp finishes, and segment lengths differ by more than 10x.
 //
 // Per nonzero the kernels move 8 B of CSR data and 16*L bytes of the dense operand (from
 // L1/L2/HBM depending on reuse); per row 4*n bytes of C.  Dense-row offsets are 64-bit.
@@ -31,40 +42,30 @@
 namespace rode {
 namespace {
 
-constexpr int kCtaThreads = 128;
-constexpr int kCtaWarps = kCtaThreads / 32;
-constexpr int kUnroll = 8;  // dense rows in flight per lane
+#ifndef RODE_SPMM_CTA_WARPS
+#define RODE_SPMM_CTA_WARPS 1
+#endif
+#ifndef RODE_SPMM_U32
+#define RODE_SPMM_U32 8
+#endif
+#ifndef RODE_SPMM_U16
+#define RODE_SPMM_U16 8
+#endif
+#ifndef RODE_SPMM_U8
+#define RODE_SPMM_U8 8
+#endif
+// Small CTAs: a CTA's slot is held until its slowest warp is done, and segments differ in
+// length by more than 10x, so fewer warps per CTA keep more warps resident on average.
+constexpr int kCtaWarps = RODE_SPMM_CTA_WARPS;
+constexpr int kCtaThreads = 32 * kCtaWarps;
 
-// acc += sum over the group's first `cnt` entries of value * B[col, slice].
-// (c, v) of entry t live in lane t of the group.  `cnt` is uniform across the group, and
-// `gmask` names exactly the lanes of the group (groups of one warp may leave early).
-template <typename T, int L>
-__device__ __forceinline__ void gather_fma(typename Vec16<T>::type &acc, int c, T v, int cnt,
-                                           const typename Vec16<T>::type *__restrict__ b_slice, size_t row_vecs,
-                                           unsigned gmask) {
-    using V = typename Vec16<T>::type;
-    constexpr int U = kUnroll < L ? kUnroll : L;
-#pragma unroll
-    for (int t0 = 0; t0 < L; t0 += U) {
-        if (t0 >= cnt) break;
-        int cc[U];
-        T vv[U];
-        V bb[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            cc[u] = __shfl_sync(gmask, c, t0 + u, L);
-            vv[u] = __shfl_sync(gmask, v, t0 + u, L);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            bb[u] = vzero(static_cast<V *>(nullptr));
-            if (t0 + u < cnt) bb[u] = ld_dense(b_slice + static_cast<size_t>(cc[u]) * row_vecs);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) vfma(acc, vv[u], bb[u]);
-    }
-}
+// Dense rows per register batch = independent 16-byte loads a lane keeps in flight.
+template <int L>
+struct Batch {
+    static constexpr int kRows = (L == 32) ? RODE_SPMM_U32 : (L == 16) ? RODE_SPMM_U16 : RODE_SPMM_U8;
+};
 
+// ---------------------------------------------------------------------------------------
 // One warp per block segment; grid.y walks the column tiles of width L * kLen.
 template <typename T, int L>
 __global__ void __launch_bounds__(kCtaThreads)
@@ -73,11 +74,14 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
            const int *__restrict__ st_off, const T *__restrict__ B, T *__restrict__ C, T *__restrict__ partial) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
+    constexpr int G = 32 / L;             // lane groups, each takes every G-th nonzero
+    constexpr int U = Batch<L>::kRows;    // rows per batch
+    constexpr int NB = (L + U - 1) / U;   // batches per 32-nonzero chunk
+    constexpr unsigned kFull = 0xffffffffu;
     const int seg = blockIdx.x * kCtaWarps + (threadIdx.x >> 5);
     if (seg >= m1) return;
     const int lane = threadIdx.x & 31;
     const int g = lane / L, l = lane % L;
-    const unsigned gmask = group_mask<L>(lane);
 
     const int row = __ldg(block_r_ind + seg);
     const int off = __ldg(st_off + seg);
@@ -88,34 +92,55 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     const bool whole_row = (off == row_begin) && (next >= row_end);
 
     const size_t row_vecs = static_cast<size_t>(n) / kLen;
-    const V *b_slice = reinterpret_cast<const V *>(B) + static_cast<size_t>(blockIdx.y) * L + l;
+    const size_t col_vec = static_cast<size_t>(blockIdx.y) * L + l;
+    const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
+
+    // (column, value) of this lane's nonzero in the current and in the next chunk
+    int c_cur = 0, c_nxt = 0;
+    T v_cur = T(0), v_nxt = T(0);
+    if (off + lane < end) {
+        c_cur = ld_stream(column_indices + off + lane);
+        v_cur = ld_stream(values + off + lane);
+    }
+    if (off + 32 + lane < end) {
+        c_nxt = ld_stream(column_indices + off + 32 + lane);
+        v_nxt = ld_stream(values + off + 32 + lane);
+    }
 
     V acc = vzero(static_cast<V *>(nullptr));
-    int e = off + lane;
-    int c = 0;
-    T v = T(0);
-    if (e < end) {
-        c = ld_stream(column_indices + e);
-        v = ld_stream(values + e);
-    }
     for (int base = off; base < end; base += 32) {
-        const int cur_c = c;
-        const T cur_v = v;
-        e += 32;
-        c = 0;
-        v = T(0);
-        if (e < end) {  // prefetch the next chunk while this one is gathered
-            c = ld_stream(column_indices + e);
-            v = ld_stream(values + e);
+        const int cnt = min(32, end - base);
+        int c_pre = 0;
+        T v_pre = T(0);
+        if (base + 64 + lane < end) {  // pairs of the chunk after next
+            c_pre = ld_stream(column_indices + base + 64 + lane);
+            v_pre = ld_stream(values + base + 64 + lane);
         }
-        const int cnt = min(L, max(0, end - base - g * L));
-        gather_fma<T, L>(acc, cur_c, cur_v, cnt, b_slice, row_vecs, gmask);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            if (b * U * G >= cnt) break;  // warp-uniform
+            V buf[U];
+            T vv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = (b * U + u) * G + g;  // position inside the chunk
+                const int c = __shfl_sync(kFull, c_cur, t);
+                vv[u] = __shfl_sync(kFull, v_cur, t);
+                buf[u] = vzero(static_cast<V *>(nullptr));
+                if (t < cnt) buf[u] = ld_dense(b_lane + static_cast<size_t>(c) * row_vecs);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) vfma(acc, vv[u], buf[u]);
+        }
+        c_cur = c_nxt;
+        v_cur = v_nxt;
+        c_nxt = c_pre;
+        v_nxt = v_pre;
     }
 #pragma unroll
-    for (int w = L; w < 32; w <<= 1) vadd(acc, vshfl_xor(0xffffffffu, acc, w));
+    for (int w = L; w < 32; w <<= 1) vadd(acc, vshfl_xor(kFull, acc, w));
 
     if (g == 0) {
-        const size_t col_vec = static_cast<size_t>(blockIdx.y) * L + l;
         if (whole_row)
             st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec, acc);
         else
@@ -123,49 +148,224 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     }
 }
 
-// Sums the workspace slots of every row that was cut into several segments.  One warp
-// looks at 32 consecutive segments; a lane whose segment is the first of a split row flags
-// it, and the warp then adds that row's slots in segment order.
+// ---------------------------------------------------------------------------------------
+// Sums the workspace slots of every row that was cut into several segments.  A CTA looks
+// at kFixupThreads consecutive segments; a thread whose segment is the first of a split row
+// queues it, and the CTA then adds that row's slots: warp w takes slots w, w+4, ... in
+// order, partial sums are combined in warp order (fixed order: deterministic).
+constexpr int kFixupThreads = 128;
+constexpr int kFixupWarps = kFixupThreads / 32;
+
 template <typename T>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(kFixupThreads)
 spmm_fixup(int m1, int n, const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
            const int *__restrict__ st_off, const T *__restrict__ partial, T *__restrict__ C) {
-    const int lane = threadIdx.x & 31;
-    const int seg = (blockIdx.x * kCtaWarps + (threadIdx.x >> 5)) * 32 + lane;
-    bool head = false;
+    __shared__ int heads[kFixupThreads];
+    __shared__ int n_heads;
+    __shared__ double sums[kFixupWarps][128];
+    if (threadIdx.x == 0) n_heads = 0;
+    __syncthreads();
+    const int seg = blockIdx.x * kFixupThreads + threadIdx.x;
     if (seg < m1) {
         const int row = __ldg(block_r_ind + seg);
         const int off = __ldg(st_off + seg);
         const int next = (seg + 1 < m1) ? __ldg(st_off + seg + 1) : INT_MAX;
-        head = (off == __ldg(row_offsets + row)) && (next < __ldg(row_offsets + row + 1));
+        if (off == __ldg(row_offsets + row) && next < __ldg(row_offsets + row + 1))
+            heads[atomicAdd(&n_heads, 1)] = seg;  // shared-memory slot counter; each head is handled alone
     }
-    unsigned todo = __ballot_sync(0xffffffffu, head);
-    while (todo) {
-        const int src = __ffs(todo) - 1;
-        todo &= todo - 1;
-        const int first = seg - lane + src;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int total = n_heads;
+    for (int h = 0; h < total; ++h) {
+        const int first = heads[h];
         const int row = __ldg(block_r_ind + first);
         int last = first + 1;
         while (last < m1 && __ldg(block_r_ind + last) == row) ++last;
-        for (int x = lane; x < n; x += 32) {
-            double sum = 0.0;
-            for (int s = first; s < last; ++s) sum += static_cast<double>(partial[static_cast<size_t>(s) * n + x]);
-            C[static_cast<size_t>(row) * n + x] = static_cast<T>(sum);
+        for (int x0 = 0; x0 < n; x0 += 128) {  // 128 columns per pass, 4 per lane
+            double acc[4] = {0.0, 0.0, 0.0, 0.0};
+            const int x = x0 + lane * 4;
+            if (x < n) {
+#pragma unroll 4
+                for (int s = first + warp; s < last; s += kFixupWarps) {
+                    const T *src = partial + static_cast<size_t>(s) * n + x;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[j] += static_cast<double>(src[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sums[warp][lane * 4 + j] = acc[j];
+            __syncthreads();
+            if (warp == 0 && x < n) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    double t = 0.0;
+#pragma unroll
+                    for (int w = 0; w < kFixupWarps; ++w) t += sums[w][lane * 4 + j];
+                    C[static_cast<size_t>(row) * n + x + j] = static_cast<T>(t);
+                }
+            }
+            __syncthreads();
         }
     }
 }
 
-// One L-lane group per residue row without a block part.
+// ---------------------------------------------------------------------------------------
+// Residue rows without a block part.  One lane group per L consecutive entries of
+// residue_r_ind; grid.y walks the column tiles.
 template <typename T, int L>
 __global__ void __launch_bounds__(kCtaThreads)
-spmm_residue(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
-             const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind,
-             const T *__restrict__ B, T *__restrict__ C) {
+spmm_rows(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
+          const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind, const T *__restrict__ B,
+          T *__restrict__ C) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
-    constexpr int kAlign = 4;   // vec_len of the preprocessing
-    constexpr int kBlockK = 32; // k_block of the preprocessing
-    const int item = (blockIdx.x * kCtaThreads + threadIdx.x) / L;
+    constexpr int U = (Batch<L>::kRows < L) ? Batch<L>::kRows : L;  // rows per batch
+    constexpr int NB = (L + U - 1) / U;  // batches per L-nonzero chunk
+    constexpr int kAlign = 4;            // vec_len of the preprocessing
+    constexpr int kBlockK = 32;          // k_block of the preprocessing
+    const int item0 = ((blockIdx.x * kCtaThreads + threadIdx.x) / L) * L;
+    if (item0 >= m2) return;  // the whole group leaves
+    const int lane = threadIdx.x & 31;
+    const int l = lane % L;
+    const unsigned gmask = group_mask<L>(lane);
+    const int gshift = lane & ~(L - 1);
+
+    // ---- descriptors: lane j of the group owns residue row item0 + j -----------------------
+    int row = 0, begin = 0, len = 0;
+    bool listed = false;  // row is this kernel's to store
+    if (item0 + l < m2) {
+        row = __ldg(residue_r_ind + item0 + l);
+        begin = __ldg(row_offsets + row);
+        const int end = __ldg(row_offsets + row + 1);
+        // aligned length >= k_block: a block part exists and its last segment took the tail
+        if (end - begin + (begin % kAlign) < kBlockK) {
+            listed = true;
+            len = end - begin;
+        }
+    }
+    int start = len;  // exclusive prefix sum of len inside the group
+#pragma unroll
+    for (int d = 1; d < L; d <<= 1) {
+        const int up = __shfl_up_sync(gmask, start, d, L);
+        if (l >= d) start += up;
+    }
+    const int total = __shfl_sync(gmask, start, L - 1, L);
+    start -= len;
+
+    const size_t row_vecs = static_cast<size_t>(n) / kLen;
+    const size_t col_vec = static_cast<size_t>(blockIdx.y) * L + l;
+    const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
+    V *c_lane = reinterpret_cast<V *>(C) + col_vec;
+
+    // ---- empty rows of the list: zeros ----------------------------------------------------------
+    unsigned zeros = (__ballot_sync(gmask, listed && len == 0) & gmask) >> gshift;
+    while (zeros) {
+        const int j = __ffs(zeros) - 1;
+        zeros &= zeros - 1;
+        const int r = __shfl_sync(gmask, row, j, L);
+        st_stream(c_lane + static_cast<size_t>(r) * row_vecs, vzero(static_cast<V *>(nullptr)));
+    }
+    unsigned todo = (__ballot_sync(gmask, len > 0) & gmask) >> gshift;  // rows with nonzeros, in order
+    if (todo == 0) return;
+
+    // ---- entry stream: position p -> nonzero index -------------------------------------------------
+    auto fetch = [&](int p, int &c, T &v) {  // all lanes of the group call
+        int lo = 0;
+#pragma unroll
+        for (int step = L / 2; step >= 1; step >>= 1) {
+            const int s = __shfl_sync(gmask, start, lo + step, L);
+            if (s <= p) lo += step;
+        }
+        const int b0 = __shfl_sync(gmask, begin, lo, L);
+        const int s0 = __shfl_sync(gmask, start, lo, L);
+        c = 0;
+        v = T(0);
+        if (p < total) {
+            c = ld_stream(column_indices + b0 + (p - s0));
+            v = ld_stream(values + b0 + (p - s0));
+        }
+    };
+    int c_cur, c_nxt;
+    T v_cur, v_nxt;
+    fetch(l, c_cur, v_cur);
+    fetch(L + l, c_nxt, v_nxt);
+
+    // ---- consumer state: the row being accumulated -------------------------------------------------
+    int cur = __ffs(todo) - 1;
+    todo &= todo - 1;
+    int cur_row = __shfl_sync(gmask, row, cur, L);
+    int cur_end = __shfl_sync(gmask, start, cur, L) + __shfl_sync(gmask, len, cur, L);
+    int pos = 0;
+    V acc = vzero(static_cast<V *>(nullptr));
+
+    for (int base = 0; base < total; base += L) {
+        const int cnt = min(L, total - base);
+        int c_pre;
+        T v_pre;
+        fetch(base + 2 * L + l, c_pre, v_pre);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            if (b * U >= cnt) break;  // group-uniform
+            V buf[U];
+            T vv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = b * U + u;  // position inside the chunk
+                const int c = __shfl_sync(gmask, c_cur, t, L);
+                vv[u] = __shfl_sync(gmask, v_cur, t, L);
+                buf[u] = vzero(static_cast<V *>(nullptr));
+                if (t < cnt) buf[u] = ld_dense(b_lane + static_cast<size_t>(c) * row_vecs);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                vfma(acc, vv[u], buf[u]);
+                ++pos;
+                if (pos == cur_end) {  // the stream passed the end of a row: store it, start the next
+                    st_stream(c_lane + static_cast<size_t>(cur_row) * row_vecs, acc);
+                    acc = vzero(static_cast<V *>(nullptr));
+                    if (todo) {
+                        cur = __ffs(todo) - 1;
+                        todo &= todo - 1;
+                        cur_row = __shfl_sync(gmask, row, cur, L);
+                        cur_end = __shfl_sync(gmask, start, cur, L) + __shfl_sync(gmask, len, cur, L);
+                    } else {
+                        cur_end = INT_MAX;
+                    }
+                }
+            }
+        }
+        c_cur = c_nxt;
+        v_cur = v_nxt;
+        c_nxt = c_pre;
+        v_nxt = v_pre;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Residue rows without a block part, one lane group per row (no batching of rows).  Used for
+// L = 8 and 16: there the lane groups of a warp would run different entry streams in
+// spmm_rows and diverge, which measured slower (stencil N = 64: 1.43 ms against 0.93 ms;
+// power-law N = 32: 331 us against 283 us) while for L = 32 the batched kernel wins
+// (R-MAT N = 128: 327 us against 770 us).
+#ifndef RODE_SPMM_ROWS_CTA
+#define RODE_SPMM_ROWS_CTA 64
+#endif
+#ifndef RODE_SPMM_ROWS_SIMPLE_MASK
+#define RODE_SPMM_ROWS_SIMPLE_MASK 3  // bit 0: L = 8, bit 1: L = 16, bit 2: L = 32
+#endif
+constexpr int kRowsCtaThreads = RODE_SPMM_ROWS_CTA;
+
+template <typename T, int L>
+__global__ void __launch_bounds__(kRowsCtaThreads)
+spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
+                 const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind,
+                 const T *__restrict__ B, T *__restrict__ C) {
+    using V = typename Vec16<T>::type;
+    constexpr int kLen = Vec16<T>::kLen;
+    constexpr int U = 8 < L ? 8 : L;
+    constexpr int kAlign = 4;
+    constexpr int kBlockK = 32;
+    const int item = (blockIdx.x * kRowsCtaThreads + threadIdx.x) / L;
     if (item >= m2) return;
     const int lane = threadIdx.x & 31;
     const int l = lane % L;
@@ -174,13 +374,11 @@ spmm_residue(int m2, int n, const T *__restrict__ values, const int *__restrict_
     const int row = __ldg(residue_r_ind + item);
     const int begin = __ldg(row_offsets + row);
     const int end = __ldg(row_offsets + row + 1);
-    // Aligned length >= k_block: the row has a block part, whose last segment already
-    // consumed the tail (see spmm_block).
     if (end - begin + (begin % kAlign) >= kBlockK) return;
 
     const size_t row_vecs = static_cast<size_t>(n) / kLen;
     const size_t col_vec = static_cast<size_t>(blockIdx.y) * L + l;
-    const V *b_slice = reinterpret_cast<const V *>(B) + col_vec;
+    const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
 
     V acc = vzero(static_cast<V *>(nullptr));
     for (int base = begin; base < end; base += L) {
@@ -191,7 +389,26 @@ spmm_residue(int m2, int n, const T *__restrict__ values, const int *__restrict_
             c = ld_stream(column_indices + e);
             v = ld_stream(values + e);
         }
-        gather_fma<T, L>(acc, c, v, min(L, end - base), b_slice, row_vecs, gmask);
+        const int cnt = min(L, end - base);
+#pragma unroll
+        for (int t0 = 0; t0 < L; t0 += U) {
+            if (t0 >= cnt) break;
+            int cc[U];
+            T vv[U];
+            V bb[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                cc[u] = __shfl_sync(gmask, c, t0 + u, L);
+                vv[u] = __shfl_sync(gmask, v, t0 + u, L);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                bb[u] = vzero(static_cast<V *>(nullptr));
+                if (t0 + u < cnt) bb[u] = ld_dense(b_lane + static_cast<size_t>(cc[u]) * row_vecs);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) vfma(acc, vv[u], bb[u]);
+        }
     }
     st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec, acc);
 }
@@ -207,16 +424,22 @@ int launch_width(int m1, int m2, int n, const T *values, const int *col, const i
         spmm_block<T, L><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets, block_r_ind, st_off, B,
                                                        C, partial);
         RODE_CHECK_LAUNCH("rode::spmm_block");
-        const int per_cta = kCtaWarps * 32;
-        spmm_fixup<T><<<(m1 + per_cta - 1) / per_cta, kCtaThreads, 0, s1>>>(m1, n, row_offsets, block_r_ind,
-                                                                            st_off, partial, C);
+        spmm_fixup<T><<<(m1 + kFixupThreads - 1) / kFixupThreads, kFixupThreads, 0, s1>>>(
+            m1, n, row_offsets, block_r_ind, st_off, partial, C);
         RODE_CHECK_LAUNCH("rode::spmm_fixup");
     }
     if (m2 > 0) {
-        constexpr int kRowsPerCta = kCtaThreads / L;
-        dim3 grid((m2 + kRowsPerCta - 1) / kRowsPerCta, tiles);
-        spmm_residue<T, L><<<grid, kCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets, residue_r_ind, B, C);
-        RODE_CHECK_LAUNCH("rode::spmm_residue");
+        constexpr int kBit = (L == 8) ? 1 : (L == 16) ? 2 : 4;
+        if (RODE_SPMM_ROWS_SIMPLE_MASK & kBit) {
+            constexpr int kRowsPerCta = kRowsCtaThreads / L;
+            dim3 grid((m2 + kRowsPerCta - 1) / kRowsPerCta, tiles);
+            spmm_rows_simple<T, L><<<grid, kRowsCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets, residue_r_ind,
+                                                                      B, C);
+        } else {
+            dim3 grid((m2 + kCtaThreads - 1) / kCtaThreads, tiles);  // a CTA covers kCtaThreads rows of the list
+            spmm_rows<T, L><<<grid, kCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets, residue_r_ind, B, C);
+        }
+        RODE_CHECK_LAUNCH("rode::spmm_rows");
     }
     return RODE_OK;
 }
@@ -257,6 +480,7 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
 }
 
 }  // namespace
+
 }  // namespace rode
 
 extern "C" {
