@@ -38,6 +38,10 @@ N_DENSE = 128
 K_SDDMM = 64
 METRIC = "SpMM GFLOP/s (2*nnz*N), fp32"
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes of ONE rode::spmm_block launch of the headline workload, keyed by R-MAT scale,
+# from an ncu capture of `python bench.py --only spmm --family rmat --scale S --width 128`
+# (summarised in profiles/); None until captured.
+NCU_TRAFFIC_BYTES = {}
 
 
 def parse_args():
@@ -200,9 +204,10 @@ def reference_arm(args, rank, world):
     A = W.rmat(scale=scale, device="cpu")
     B = W.dense(A.n, N_DENSE, seed=3).numpy()
     rp, col, val = A.row_ptr.numpy(), A.col.numpy(), A.val.numpy()
-    for _ in range(max(1, min(args.warmup, 1))):
+    warm = max(1, min(args.warmup, 3))
+    for _ in range(warm):
         cpu.spmm_f32(rp, col, val, B, threads=threads)
-    steps = max(1, min(args.steps, 5))
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu.spmm_f32(rp, col, val, B, threads=threads)
@@ -211,7 +216,7 @@ def reference_arm(args, rank, world):
     sample = f"R-MAT scale {scale} (nnz {A.nnz}), N={N_DENSE}, full pass per step"
     line = {
         "impl": "reference", "metric": METRIC, "value": gflops, "unit": "GFLOP/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "steps": steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"rmat{args.scale}_spmm_n{N_DENSE}", "sample": sample},
         "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": threads, "kind": "port", "sample": sample},
@@ -522,7 +527,7 @@ def main():
     block_bytes_all = sum_over_ranks(float(block_bytes))
     step_bytes_all = sum_over_ranks(float(spmm_bmin(my_nnz, my_rows, N_DENSE, kt_all)))
     roofline = {
-        "kernel": "rode::spmm_block<float,32> (+ spmm_fixup on the same stream)",
+        "kernel": "rode::spmm_block<float,32> (timed with spmm_fixup, which follows it on the same stream)",
         "bound": "hbm", "achieved": block_bytes_all / world / ms_block / 1e6 if ms_block else None,
         "peak": peak_gbs, "unit": "GB/s", "peak_kind": f"of {peak_kind}",
         "frac": (block_bytes_all / world / ms_block / 1e6 / peak_gbs) if ms_block else None,
@@ -531,12 +536,9 @@ def main():
         "step": {"algorithmic_bytes": step_bytes_all, "achieved": step_bytes_all / ms_step / 1e6,
                  "frac": step_bytes_all / ms_step / 1e6 / (peak_gbs * world)},
     }
-    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_path):
-        try:
-            roofline["traffic"] = json.load(open(traffic_path)).get("spmm_block_rmat23_n128_bytes_per_launch")
-        except Exception:
-            pass
+    if world == 1 and args.scale in NCU_TRAFFIC_BYTES:
+        roofline["traffic"] = NCU_TRAFFIC_BYTES[args.scale]
+        roofline["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one spmm_block launch on this workload"
 
     # ---- SDDMM K = 64 on the same rows ---------------------------------------------------------
     lhs = W.dense(n_vert, K_SDDMM, device=dev, seed=5)[r0:r1].contiguous()
@@ -600,14 +602,23 @@ def main():
         from oracle import cpu
 
         threads = cpu.max_threads()
-        rows_sample = min(my_rows, 1 << 20)             # first 2^20 rows of the same matrix, full width
-        rp_s = h_rp[: rows_sample + 1].numpy()
-        nnz_s = int(rp_s[-1])
-        t0 = time.perf_counter()
-        cpu.spmm_f32(rp_s, h_col.numpy()[:nnz_s], h_val.numpy()[:nnz_s], h_X.numpy(), threads=threads)
-        dt = time.perf_counter() - t0
-        cpu_baseline = {"value": 2.0 * nnz_s * N_DENSE / dt / 1e9, "unit": "GFLOP/s", "cores": threads, "kind": "port",
-                        "sample": f"rows 0..{rows_sample} of the headline matrix (nnz {nnz_s}), one pass, {dt:.2f} s",
+        # all host threads: whole passes over the headline matrix for about 10 s
+        rp_h, col_h, val_h, X_h = h_rp.numpy(), h_col.numpy(), h_val.numpy(), h_X.numpy()
+        passes, t0 = 0, time.perf_counter()
+        while passes < 40 and (passes == 0 or time.perf_counter() - t0 < 10.0):
+            cpu.spmm_f32(rp_h, col_h, val_h, X_h, threads=threads)
+            passes += 1
+        dt = (time.perf_counter() - t0) / passes
+        # one thread (how the reference's own CPU code runs): the first 2^18 rows, one pass
+        rows_1 = min(my_rows, 1 << 18)
+        nnz_1 = int(rp_h[rows_1])
+        t1 = time.perf_counter()
+        cpu.spmm_f32(rp_h[: rows_1 + 1], col_h[:nnz_1], val_h[:nnz_1], X_h, threads=1)
+        dt1 = time.perf_counter() - t1
+        cpu_baseline = {"value": 2.0 * my_nnz * N_DENSE / dt / 1e9, "unit": "GFLOP/s", "cores": threads, "kind": "port",
+                        "sample": f"{passes} full passes over the headline matrix (nnz {my_nnz}), {dt:.3f} s per pass",
+                        "single_thread_value": 2.0 * nnz_1 * N_DENSE / dt1 / 1e9,
+                        "single_thread_sample": f"rows 0..{rows_1} (nnz {nnz_1}), one pass, {dt1:.2f} s",
                         "note": "the reference has no CPU SpMM; this is the oracle's CSR SpMM with OpenMP over rows"}
         del h_rp, h_col, h_val, h_X, h_C, d_rp, d_col, d_val, d_X
         torch.cuda.empty_cache()
