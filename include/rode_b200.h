@@ -81,6 +81,33 @@ int rode_preprocess(int seg_len, int k_block, int vec_len, int M, const int *row
                     int *block_r_ind, int *st_off, int *residue_r_ind, int *n_blk, int *n_res,
                     void *workspace, size_t workspace_bytes, rode_stream_t stream);
 
+/* Same decomposition, same outputs, but the library allocates nothing and the caller brings
+ * no workspace: the per-tile scratch lives in a fixed array inside the library's device
+ * image (128 KB on every GPU that loads the library, kept until the process exits).
+ * This entry point has no counterpart in the reference.
+ *
+ * It is meant for callers that must not, or cannot, obtain device memory at call time:
+ * a process that has handed the whole GPU to its own memory pool (a serving engine's
+ * arena, a framework's caching allocator with a hard cap), where a cudaMalloc issued by a
+ * library can fail or fragment the pool; and callers inside a latency-critical loop, where
+ * cudaMalloc / cudaFree would synchronise the whole device and stall every other stream.
+ * Those callers also cannot use RoDe_preprocess (it grows a library-owned buffer with
+ * cudaMalloc on first use) and may have no spare buffer to pass to rode_preprocess.
+ *
+ *   Limit     M <= 16,777,216 rows (2^24); larger M returns RODE_ERR_INVALID_ARGUMENT with a
+ *             message, before anything is launched.
+ *   Set-up    the first call on each device looks up the array's device address (the
+ *             device must be current, as for every call); make that first call before any
+ *             stream capture begins.  No cudaMalloc, cudaFree or other allocating routine
+ *             is called, then or later.
+ *   Sharing   all calls on a device use the same array and it keeps the previous call's
+ *             contents.  Nothing needs clearing (every entry that is read is written first
+ *             by the same call), but two calls that overlap in time on one GPU, e.g. on
+ *             two streams, race on it: serialise them. */
+int rode_preprocess_noalloc(int seg_len, int k_block, int vec_len, int M, const int *row_ptr,
+                            int *block_r_ind, int *st_off, int *residue_r_ind, int *n_blk, int *n_res,
+                            rode_stream_t stream);
+
 /* Host twin with HOST pointers, replacing RoDe_preprocess_cpu
  * (Preprocess_opt/_preprocess.cu:340-373) and the host loops of
  * RoDe_SDDMM/main.cu:114-163.  Part of the reference's API surface; it is not a fallback

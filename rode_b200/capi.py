@@ -25,7 +25,7 @@ RODE_ERR_NO_DEVICE = 4
 # Every symbol include/rode_b200.h declares.
 C_ABI_SYMBOLS = (
     "rode_last_error", "rode_version", "rode_preprocess_workspace_bytes", "rode_preprocess_capacity",
-    "rode_preprocess", "rode_preprocess_cpu", "rode_spmm_workspace_bytes", "rode_spmm_f32", "rode_spmm_f64",
+    "rode_preprocess", "rode_preprocess_noalloc", "rode_preprocess_cpu", "rode_spmm_workspace_bytes", "rode_spmm_f32", "rode_spmm_f64",
     "rode_sddmm_f32",
 )
 # Itanium-ABI names of the C++ entry points declared in RoDeSpmm.h / RoDeSddmm.h /
@@ -69,13 +69,14 @@ def load() -> ctypes.CDLL:
     lib.rode_preprocess_workspace_bytes.argtypes = [ci, ctypes.POINTER(sz)]
     lib.rode_preprocess_capacity.argtypes = [ci, ci, ci, ctypes.c_longlong, ctypes.POINTER(ctypes.c_longlong)]
     lib.rode_preprocess.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.rode_preprocess_noalloc.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp]
     lib.rode_preprocess_cpu.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]
     lib.rode_spmm_workspace_bytes.argtypes = [ci, ci, ci, ctypes.POINTER(sz)]
     lib.rode_spmm_f32.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp, vp]
     lib.rode_spmm_f64.argtypes = lib.rode_spmm_f32.argtypes
     lib.rode_sddmm_f32.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     for name in ("rode_preprocess_workspace_bytes", "rode_preprocess_capacity", "rode_preprocess",
-                 "rode_preprocess_cpu", "rode_spmm_workspace_bytes", "rode_spmm_f32", "rode_spmm_f64",
+                 "rode_preprocess_noalloc", "rode_preprocess_cpu", "rode_spmm_workspace_bytes", "rode_spmm_f32", "rode_spmm_f64",
                  "rode_sddmm_f32"):
         getattr(lib, name).restype = ci
     _lib = lib
@@ -141,6 +142,14 @@ def preprocess_raw(seg_len, k_block, vec_len, M, row_ptr, block_r_ind, st_off, r
     """rode_preprocess on raw device addresses (ints) or tensors' data_ptr()."""
     check(load().rode_preprocess(seg_len, k_block, vec_len, M, row_ptr, block_r_ind, st_off, residue_r_ind, n_blk,
                                  n_res, workspace, workspace_bytes, _stream(stream)))
+
+
+def preprocess_noalloc_raw(seg_len, k_block, vec_len, M, row_ptr, block_r_ind, st_off, residue_r_ind, n_blk, n_res,
+                           stream=None) -> None:
+    """rode_preprocess_noalloc on raw device addresses: the variant for callers that cannot
+    allocate device memory (scratch is a fixed array inside the library, M <= 2**24)."""
+    check(load().rode_preprocess_noalloc(seg_len, k_block, vec_len, M, row_ptr, block_r_ind, st_off, residue_r_ind,
+                                         n_blk, n_res, _stream(stream)))
 
 
 def preprocess(row_ptr: torch.Tensor, nnz: int, seg_len: int = 512, k_block: int = 32, vec_len: int = 4,

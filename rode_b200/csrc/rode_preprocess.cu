@@ -18,6 +18,8 @@
 //
 // HBM traffic: row_ptr is read twice (8 B/row), outputs written once (8 B/segment,
 // 4 B/residue row), scratch is 8 B per 1024 rows.
+#include <mutex>
+
 #include "rode_common.cuh"
 
 namespace rode {
@@ -244,6 +246,31 @@ int launch_preprocess(int seg_len, int k_block, int vec_len, int M, const int *r
 
 int preprocess_tiles(int M) { return (M + kTile - 1) / kTile; }
 
+// ---------------------------------------------------------------------------------------
+// Scratch of rode_preprocess_noalloc: one int2 per tile for up to kNoAllocMaxRows rows,
+// resident in every GPU that loads the library (128 KB) until the process exits.  In host
+// code this name is only a handle; the device address comes from cudaGetSymbolAddress.
+constexpr int kNoAllocMaxRows = 1 << 24;
+constexpr int kNoAllocTiles = kNoAllocMaxRows / kTile;
+static __device__ __align__(256) int2 g_noalloc_tile_scratch[kNoAllocTiles];
+
+// Device address of the scratch array on the current device, looked up once per device.
+int noalloc_scratch(int2 **out) {
+    static int2 *address[64] = {nullptr};
+    static std::mutex lock;
+    int dev = 0;
+    RODE_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(RODE_ERR_NO_DEVICE, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> guard(lock);
+    if (address[dev] == nullptr) {
+        void *p = nullptr;
+        RODE_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_tile_scratch));
+        address[dev] = static_cast<int2 *>(p);
+    }
+    *out = address[dev];
+    return RODE_OK;
+}
+
 }  // namespace rode
 
 extern "C" {
@@ -278,6 +305,23 @@ int rode_preprocess(int seg_len, int k_block, int vec_len, int M, const int *row
         return rode::fail(RODE_ERR_WORKSPACE, "preprocess: workspace must be 8-byte aligned");
     return rode::launch_preprocess(seg_len, k_block, vec_len, M, row_ptr, block_r_ind, st_off, residue_r_ind,
                                    n_blk, n_res, static_cast<int2 *>(workspace), stream);
+}
+
+int rode_preprocess_noalloc(int seg_len, int k_block, int vec_len, int M, const int *row_ptr, int *block_r_ind,
+                            int *st_off, int *residue_r_ind, int *n_blk, int *n_res, rode_stream_t stream) {
+    if (int rc = rode::check_params(seg_len, k_block, vec_len, M, row_ptr)) return rc;
+    if (!block_r_ind || !st_off || !residue_r_ind || !n_blk || !n_res)
+        return rode::fail(RODE_ERR_INVALID_ARGUMENT, "preprocess_noalloc: an output pointer is null");
+    if (M > rode::kNoAllocMaxRows)
+        return rode::fail(RODE_ERR_INVALID_ARGUMENT,
+                          "preprocess_noalloc: M = %d exceeds the built-in scratch (at most %d rows); use "
+                          "rode_preprocess with a caller-provided workspace",
+                          M, rode::kNoAllocMaxRows);
+    int2 *scratch = nullptr;
+    if (int rc = rode::noalloc_scratch(&scratch)) return rc;
+    // count_tiles rewrites every tile total it later reads, so nothing has to be cleared.
+    return rode::launch_preprocess(seg_len, k_block, vec_len, M, row_ptr, block_r_ind, st_off, residue_r_ind,
+                                   n_blk, n_res, scratch, stream);
 }
 
 int rode_preprocess_cpu(int seg_len, int k_block, int vec_len, int M, const int *row_ptr, int *block_r_ind,
