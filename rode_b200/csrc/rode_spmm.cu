@@ -66,16 +66,18 @@ struct Batch {
 };
 
 // ---------------------------------------------------------------------------------------
-// One warp per block segment; grid.y walks the column tiles of width L * kLen.
-template <typename T, int L>
-__global__ void __launch_bounds__(kCtaThreads)
+// One warp per block segment; grid.y walks the column tiles of width L * kLen.  U = dense
+// rows per batch (loads in flight per lane): 8 for grids that fill the GPU (64 registers keep
+// 32 warps per SM resident); the whole chunk (U = L) for small grids, where the time is the
+// dependent-batch chain of the longest segment and registers are free.
+template <typename T, int L, int U>
+__global__ void __launch_bounds__(kCtaThreads, (U > Batch<L>::kRows) ? 1 : 32 / kCtaWarps)
 spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
            const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
            const int *__restrict__ st_off, const T *__restrict__ B, T *__restrict__ C, T *__restrict__ partial) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
     constexpr int G = 32 / L;             // lane groups, each takes every G-th nonzero
-    constexpr int U = Batch<L>::kRows;    // rows per batch
     constexpr int NB = (L + U - 1) / U;   // batches per 32-nonzero chunk
     constexpr unsigned kFull = 0xffffffffu;
     const int seg = blockIdx.x * kCtaWarps + (threadIdx.x >> 5);
@@ -149,62 +151,79 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------
-// Sums the workspace slots of every row that was cut into several segments.  A CTA looks
-// at kFixupThreads consecutive segments; a thread whose segment is the first of a split row
-// queues it, and the CTA then adds that row's slots: warp w takes slots w, w+4, ... in
-// order, partial sums are combined in warp order (fixed order: deterministic).
-constexpr int kFixupThreads = 128;
-constexpr int kFixupWarps = kFixupThreads / 32;
+// Sums the workspace slots of every row that was cut into several segments.  A one-warp CTA
+// looks at 32 consecutive segments; a lane whose segment is the first of a split row flags
+// it, and the warp then adds that row's slots (fp64 accumulation, eight slots in flight per
+// lane; the order is fixed by the code, so the result is deterministic).
+constexpr int kFixupThreads = 32;
+constexpr int kFixupUnroll = 8;  // workspace slots in flight per lane
 
 template <typename T>
 __global__ void __launch_bounds__(kFixupThreads)
 spmm_fixup(int m1, int n, const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
            const int *__restrict__ st_off, const T *__restrict__ partial, T *__restrict__ C) {
-    __shared__ int heads[kFixupThreads];
-    __shared__ int n_heads;
-    __shared__ double sums[kFixupWarps][128];
-    if (threadIdx.x == 0) n_heads = 0;
-    __syncthreads();
-    const int seg = blockIdx.x * kFixupThreads + threadIdx.x;
+    constexpr unsigned kFull = 0xffffffffu;
+    const int lane = threadIdx.x;
+    const int seg = blockIdx.x * 32 + lane;
+    bool head = false;
+    int row = 0, count = 0;
     if (seg < m1) {
-        const int row = __ldg(block_r_ind + seg);
+        row = __ldg(block_r_ind + seg);
         const int off = __ldg(st_off + seg);
         const int next = (seg + 1 < m1) ? __ldg(st_off + seg + 1) : INT_MAX;
-        if (off == __ldg(row_offsets + row) && next < __ldg(row_offsets + row + 1))
-            heads[atomicAdd(&n_heads, 1)] = seg;  // shared-memory slot counter; each head is handled alone
+        const int row_begin = __ldg(row_offsets + row);
+        const int row_end = __ldg(row_offsets + row + 1);
+        head = (off == row_begin) && (next < row_end);
+        if (head) {
+            // number of segments of the row = pieces of (next - aligned start) nonzeros
+            const int piece = next - (row_begin - row_begin % 4);
+            count = (row_end - (row_begin - row_begin % 4) + piece - 1) / piece;
+            // the last piece is a segment only if it is >= 32 long; otherwise it was a
+            // residue tail that the previous segment consumed
+            const int last_len = row_end - (row_begin - row_begin % 4) - (count - 1) * piece;
+            if (last_len < 32) --count;
+        }
     }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int total = n_heads;
-    for (int h = 0; h < total; ++h) {
-        const int first = heads[h];
-        const int row = __ldg(block_r_ind + first);
-        int last = first + 1;
-        while (last < m1 && __ldg(block_r_ind + last) == row) ++last;
-        for (int x0 = 0; x0 < n; x0 += 128) {  // 128 columns per pass, 4 per lane
+    unsigned todo = __ballot_sync(kFull, head);
+    while (todo) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        const int first = blockIdx.x * 32 + src;
+        const int r = __shfl_sync(kFull, row, src);
+        const int cnt = __shfl_sync(kFull, count, src);
+        // 4 columns per lane.  Rows narrower than 128 columns leave lanes over: those form
+        // 32 / (n/4) groups that take alternate slots and are combined by shuffles.
+        const int quads = n / 4;
+        const int width = (quads == 8 || quads == 16) ? quads : 32;  // lanes per slot
+        const int groups = 32 / width;
+        const int g = lane / width, l = lane % width;
+        for (int x = l * 4; x < n; x += 128) {
             double acc[4] = {0.0, 0.0, 0.0, 0.0};
-            const int x = x0 + lane * 4;
-            if (x < n) {
-#pragma unroll 4
-                for (int s = first + warp; s < last; s += kFixupWarps) {
-                    const T *src = partial + static_cast<size_t>(s) * n + x;
+            for (int s0 = g; s0 < cnt; s0 += groups * kFixupUnroll) {
+                T v[kFixupUnroll][4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[j] += static_cast<double>(src[j]);
+                for (int u = 0; u < kFixupUnroll; ++u) {
+                    const int s = s0 + u * groups;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[u][j] = T(0);
+                    if (s < cnt) {
+                        const T *src_row = partial + static_cast<size_t>(first + s) * n + x;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) v[u][j] = src_row[j];
+                    }
                 }
+#pragma unroll
+                for (int u = 0; u < kFixupUnroll; ++u)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[j] += static_cast<double>(v[u][j]);
             }
+            for (int w = width; w < 32; w <<= 1)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) sums[warp][lane * 4 + j] = acc[j];
-            __syncthreads();
-            if (warp == 0 && x < n) {
+                for (int j = 0; j < 4; ++j) acc[j] += __shfl_xor_sync(kFull, acc[j], w);
+            if (g == 0) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    double t = 0.0;
-#pragma unroll
-                    for (int w = 0; w < kFixupWarps; ++w) t += sums[w][lane * 4 + j];
-                    C[static_cast<size_t>(row) * n + x + j] = static_cast<T>(t);
-                }
+                for (int j = 0; j < 4; ++j) C[static_cast<size_t>(r) * n + x + j] = static_cast<T>(acc[j]);
             }
-            __syncthreads();
         }
     }
 }
@@ -214,17 +233,18 @@ spmm_fixup(int m1, int n, const int *__restrict__ row_offsets, const int *__rest
 // residue_r_ind; grid.y walks the column tiles.
 template <typename T, int L>
 __global__ void __launch_bounds__(kCtaThreads)
-spmm_rows(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
-          const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind, const T *__restrict__ B,
-          T *__restrict__ C) {
+spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
+          const int *__restrict__ column_indices, const int *__restrict__ row_offsets,
+          const int *__restrict__ residue_r_ind, const T *__restrict__ B, T *__restrict__ C) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
     constexpr int U = (Batch<L>::kRows < L) ? Batch<L>::kRows : L;  // rows per batch
     constexpr int NB = (L + U - 1) / U;  // batches per L-nonzero chunk
     constexpr int kAlign = 4;            // vec_len of the preprocessing
     constexpr int kBlockK = 32;          // k_block of the preprocessing
-    const int item0 = ((blockIdx.x * kCtaThreads + threadIdx.x) / L) * L;
-    if (item0 >= m2) return;  // the whole group leaves
+    const long long group = (static_cast<long long>(blockIdx.x) * kCtaThreads + threadIdx.x) / L;
+    if (group * rows_per_group >= m2) return;  // the whole group leaves
+    const int item0 = static_cast<int>(group * rows_per_group);
     const int lane = threadIdx.x & 31;
     const int l = lane % L;
     const unsigned gmask = group_mask<L>(lane);
@@ -233,7 +253,7 @@ spmm_rows(int m2, int n, const T *__restrict__ values, const int *__restrict__ c
     // ---- descriptors: lane j of the group owns residue row item0 + j -----------------------
     int row = 0, begin = 0, len = 0;
     bool listed = false;  // row is this kernel's to store
-    if (item0 + l < m2) {
+    if (l < rows_per_group && item0 + l < m2) {
         row = __ldg(residue_r_ind + item0 + l);
         begin = __ldg(row_offsets + row);
         const int end = __ldg(row_offsets + row + 1);
@@ -413,6 +433,18 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
     st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec, acc);
 }
 
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cached[dev] = v;
+    }
+    return cached[dev];
+}
+
 template <typename T, int L>
 int launch_width(int m1, int m2, int n, const T *values, const int *col, const int *row_offsets,
                  const int *block_r_ind, const int *residue_r_ind, const int *st_off, const T *B, T *C,
@@ -421,8 +453,14 @@ int launch_width(int m1, int m2, int n, const T *values, const int *col, const i
     const unsigned tiles = static_cast<unsigned>(n / kTileWidth);
     if (m1 > 0) {
         dim3 grid((m1 + kCtaWarps - 1) / kCtaWarps, tiles);
-        spmm_block<T, L><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets, block_r_ind, st_off, B,
-                                                       C, partial);
+        // fewer warps than two full waves of 32 per SM: latency of the longest segment rules
+        const bool small_grid = static_cast<long long>(m1) * tiles <= 2LL * 32 * sm_count();
+        if (small_grid && L > Batch<L>::kRows)
+            spmm_block<T, L, L><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets, block_r_ind,
+                                                              st_off, B, C, partial);
+        else
+            spmm_block<T, L, Batch<L>::kRows><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets,
+                                                                            block_r_ind, st_off, B, C, partial);
         RODE_CHECK_LAUNCH("rode::spmm_block");
         spmm_fixup<T><<<(m1 + kFixupThreads - 1) / kFixupThreads, kFixupThreads, 0, s1>>>(
             m1, n, row_offsets, block_r_ind, st_off, partial, C);
@@ -436,8 +474,16 @@ int launch_width(int m1, int m2, int n, const T *values, const int *col, const i
             spmm_rows_simple<T, L><<<grid, kRowsCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets, residue_r_ind,
                                                                       B, C);
         } else {
-            dim3 grid((m2 + kCtaThreads - 1) / kCtaThreads, tiles);  // a CTA covers kCtaThreads rows of the list
-            spmm_rows<T, L><<<grid, kCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets, residue_r_ind, B, C);
+            // L rows per lane group when the list is long; fewer (shorter dependent chains,
+            // more warps) when the groups would not fill the GPU twice over
+            const long long slots = 2LL * 28 * sm_count() * (kCtaThreads / L);
+            int per_group = static_cast<int>((m2 + slots - 1) / slots);
+            per_group = per_group < 4 ? 4 : (per_group > L ? L : per_group);
+            const long long groups = (static_cast<long long>(m2) + per_group - 1) / per_group;
+            constexpr int kGroupsPerCta = kCtaThreads / L;
+            dim3 grid(static_cast<unsigned>((groups + kGroupsPerCta - 1) / kGroupsPerCta), tiles);
+            spmm_rows<T, L><<<grid, kCtaThreads, 0, s2>>>(m2, per_group, n, values, col, row_offsets,
+                                                          residue_r_ind, B, C);
         }
         RODE_CHECK_LAUNCH("rode::spmm_rows");
     }

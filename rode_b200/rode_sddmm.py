@@ -44,6 +44,8 @@ class RoDeCSR:
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise ValueError("RoDeCSR needs a CUDA device; rode_b200 has no CPU path")
+        if self.device.index is None:  # "cuda" -> "cuda:<current>", so that tensor.device compares equal
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self.row_offsets = row_offsets.to(dtype=torch.int32, device=self.device).contiguous()
         self.row_offsets_cpu = row_offsets.to(dtype=torch.int32, device="cpu").contiguous()
         self.column_indices = column_indices.to(dtype=torch.int32, device=self.device).contiguous()

@@ -1,0 +1,102 @@
+"""The Python entry (`rode_b200.rode_sddmm`, compiled torch binding) used the way the
+reference's own Python tests use `rode_sddmm.py` (RoDe_SDDMM/test_pytorch.py: RoDeCSR.from_random
+-> rode_sddmm vs torch.sparse.sampled_addmm via compare_results, tolerance 1e-3), over the same
+kinds of shapes its runners sweep (small, prime and irregular dimensions, tall, wide, one row,
+one column, 1..512 nonzeros per row, 4096^2)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [  # (m, n, nnz_per_row)
+    (64, 64, 8), (256, 256, 32), (63, 67, 10), (127, 131, 23), (511, 517, 33), (1023, 1031, 65),
+    (2048, 256, 32), (1999, 257, 45), (256, 2048, 32), (257, 2003, 47), (1, 1000, 100), (1000, 1, 1),
+    (17, 1999, 150), (1999, 17, 5), (1024, 1024, 1), (1024, 1024, 4), (1024, 1024, 64), (1024, 1024, 512),
+    (32, 32, 16), (33, 31, 10), (4096, 4096, 128), (4093, 4099, 129),
+]
+
+
+@pytest.fixture(scope="module")
+def api():
+    from rode_b200 import rode_sddmm
+
+    return rode_sddmm
+
+
+@pytest.mark.parametrize("k", [32, 64, 128])
+def test_rode_sddmm_against_torch_sampled_addmm(api, k):
+    torch.manual_seed(42)
+    dev = torch.device("cuda")
+    for m, n, per_row in SHAPES:
+        S = api.RoDeCSR.from_random(m, n, per_row, dev, k=k)
+        assert S.row_offsets.is_cuda and S.block_indices.is_cuda and S.st_offsets.numel() == S.m1 + 1
+        lhs = torch.randn(m, k, device=dev)
+        rhs = torch.randn(n, k, device=dev)
+        out = api.rode_sddmm(S, lhs, rhs)
+        want = api.torch_sddmm_reference(S.to_torch_sparse_csr(), lhs, rhs)
+        report = api.compare_results(out, want, S, tolerance=1e-3)
+        assert report["passed"], (m, n, per_row, k, report)
+        # tighter than the reference's own 1e-3 rule: fp64 check of a few entries
+        rows = torch.repeat_interleave(torch.arange(m, device=dev), (S.row_offsets[1:] - S.row_offsets[:-1]).long())
+        idx = torch.randint(0, S.nnz, (min(S.nnz, 256),), device=dev)
+        truth = S.values[idx].double() * (lhs[rows[idx]].double() * rhs[S.column_indices[idx].long()].double()).sum(1)
+        assert torch.allclose(out[idx].double(), truth, rtol=1e-5, atol=2e-4 * (k / 32) ** 0.5)
+
+
+def test_preprocess_binding_accepts_cpu_and_cuda_row_offsets(api, oracle_cpu):
+    from rode_b200 import rode_sddmm_cuda
+
+    S = api.RoDeCSR.from_random(3000, 5000, 40, torch.device("cuda"), k=32)
+    rp_cpu = S.row_offsets_cpu
+    want = oracle_cpu.preprocess(rp_cpu.numpy(), 512, 32, 4)
+    for rp in (rp_cpu, S.row_offsets):
+        blk, st, res, m1, m2 = rode_sddmm_cuda.preprocess(rp, S.nnz, 512, 32, 4)
+        assert blk.device.type == rp.device.type and st.device.type == rp.device.type
+        assert (m1, m2) == (want[3], want[4]) and st.numel() == m1 + 1
+        assert np.array_equal(blk[:m1].cpu().numpy(), want[0])
+        assert np.array_equal(st.cpu().numpy(), want[1])
+        assert np.array_equal(res[:m2].cpu().numpy(), want[2])
+    # shapes the reference returns for an empty block list: [1], [1], [max(n_res, 1)]
+    tiny = torch.tensor([0, 3, 5], dtype=torch.int32)
+    blk, st, res, m1, m2 = rode_sddmm_cuda.preprocess(tiny, 5, 512, 32, 4)
+    assert m1 == 0 and blk.numel() == 1 and st.tolist() == [5] and res[:m2].tolist() == [0, 1]
+
+
+def test_argument_checks_mirror_the_reference(api):
+    dev = torch.device("cuda")
+    S = api.RoDeCSR.from_random(128, 96, 8, dev, k=32)
+    with pytest.raises(ValueError):
+        api.RoDeCSR(S.row_offsets_cpu, S.column_indices, S.values, dev, 128, 96, k=48)
+    with pytest.raises(ValueError):
+        api.rode_sddmm(S, torch.zeros(128, 64, device=dev), torch.zeros(96, 32, device=dev))
+    with pytest.raises(AssertionError):
+        api.rode_sddmm(S, torch.zeros(128, 32), torch.zeros(96, 32, device=dev))
+    with pytest.raises(AssertionError):
+        api.rode_sddmm(S, torch.zeros(128, 32, device=dev, dtype=torch.float64), torch.zeros(96, 32, device=dev))
+    assert "RoDeCSR(m=128, n=96" in repr(S)
+
+
+def test_rode_spmm_python_entry(api):
+    dev = torch.device("cuda")
+    torch.manual_seed(3)
+    for m, n, per_row, width in ((4096, 4096, 128, 128), (1999, 257, 45, 32), (1, 1000, 100, 64), (1000, 1, 1, 96)):
+        S = api.RoDeCSR.from_random(m, n, per_row, dev, k=32)
+        X = torch.randn(n, width, device=dev)
+        C = api.rode_spmm(S, X)
+        want = torch.sparse.mm(S.to_torch_sparse_csr().double(), X.double())
+        assert torch.allclose(C.double(), want, rtol=1e-5, atol=1e-4 * max(1.0, (per_row / 16) ** 0.5))
+
+
+def test_launches_on_the_current_stream_without_blocking(api):
+    dev = torch.device("cuda")
+    S = api.RoDeCSR.from_random(2048, 2048, 64, dev, k=128)
+    lhs, rhs = torch.randn(2048, 128, device=dev), torch.randn(2048, 128, device=dev)
+    base = api.rode_sddmm(S, lhs, rhs)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        scaled = api.rode_sddmm(S, lhs * 2, rhs)     # producer and consumer ordered on stream s
+        total = scaled.sum()
+    s.synchronize()
+    assert torch.allclose(total, 2 * base.sum(), rtol=1e-4)
