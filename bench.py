@@ -39,9 +39,10 @@ K_SDDMM = 64
 METRIC = "SpMM GFLOP/s (2*nnz*N), fp32"
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes of ONE rode::spmm_block launch of the headline workload, keyed by R-MAT scale,
-# from an ncu capture of `python bench.py --only spmm --family rmat --scale S --width 128`
-# (summarised in profiles/); None until captured.
-NCU_TRAFFIC_BYTES = {}
+# from a single-pass ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of
+# `python bench.py --only spmm --family rmat --scale S --width 128 --steps 1 --warmup 1`
+# (summarised in profiles/spmm_dram_traffic_rmat23_n128.md).
+NCU_TRAFFIC_BYTES = {23: 27331223808 + 286452992, 21: 3849421824 + 93184512}
 
 
 def parse_args():
@@ -53,6 +54,8 @@ def parse_args():
     p.add_argument("--scale", type=int, default=23, help="R-MAT scale of the headline workload")
     p.add_argument("--no-extra", action="store_true", help="skip the secondary configs and the CPU baseline")
     p.add_argument("--e2e-steps", type=int, default=3)
+    p.add_argument("--row-weight", type=float, default=1.0,
+                   help="multi-GPU partition: cost of a row = its nnz + this (0 = plain nnz-balanced)")
     p.add_argument("--only", choices=["spmm", "sddmm"], default=None,
                    help="small single-op run (one family, one width) for profiling and A/B timing")
     p.add_argument("--family", default="rmat", choices=["bernoulli", "zipf", "stencil", "pareto", "rmat"])
@@ -195,7 +198,7 @@ def reference_arm(args, rank, world):
     """CPU implementation on the host cores: the oracle's CSR SpMM (the reference ships no
     CPU SpMM), all threads, on a bounded sample of the headline workload."""
     if rank != 0:
-        return
+        return None
     from oracle import cpu
     from rode_b200 import workloads as W
 
@@ -222,7 +225,7 @@ def reference_arm(args, rank, world):
         "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gflops, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    return line
 
 
 # ---------------------------------------------------------------------------------------
@@ -380,23 +383,41 @@ def single_op(args):
         bmin = sddmm_bmin(A.nnz, A.m, width, int((lens > 0).sum()), k_touched)
     flush = torch.zeros(64 * 1024 * 1024, device=dev)
     ms = time_loop(lambda: fj.run(launch), args.steps, args.warmup, fj.cur, flush)
-    print(json.dumps({"only": args.only, "family": args.family, "width": width, "rows": A.m, "nnz": A.nnz,
-                      "m1": meta.m1, "m2": meta.m2, "ms": ms, "gflops": 2.0 * A.nnz * width / ms / 1e6,
-                      "bmin_bytes": bmin, "algorithmic_gbs": bmin / ms / 1e6,
-                      "frac": bmin / ms / 1e6 / peak_gbs, "peak_kind": peak_kind, "k_touched": k_touched}))
+    return {"only": args.only, "family": args.family, "width": width, "rows": A.m, "nnz": A.nnz,
+            "m1": meta.m1, "m2": meta.m2, "ms": ms, "gflops": 2.0 * A.nnz * width / ms / 1e6,
+            "bmin_bytes": bmin, "algorithmic_gbs": bmin / ms / 1e6,
+            "frac": bmin / ms / 1e6 / peak_gbs, "peak_kind": peak_kind, "k_touched": k_touched}
 
 
 # ---------------------------------------------------------------------------------------
+class QuietStdout:
+    """Everything the process (or a library underneath it, e.g. NCCL's version banner) writes
+    to file descriptor 1 goes to stderr; only the final JSON line goes to the real stdout."""
+
+    def __init__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+
+    def emit(self, text: str):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        print(text, flush=True)
+
+
 def main():
     args = parse_args()
+    console = QuietStdout()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        reference_arm(args, rank, world)
+        line = reference_arm(args, rank, world)
+        if line is not None:
+            console.emit(json.dumps(line))
         return
     if args.only is not None:
-        single_op(args)
+        console.emit(json.dumps(single_op(args)))
         return
 
     import torch.distributed as dist
@@ -468,7 +489,7 @@ def main():
         torch.cuda.synchronize()
         broadcast_ms = e0.elapsed_time(e1)
     full = W.CSR(n_vert, n_vert, row_ptr, col, val)
-    bounds = W.partition_rows(row_ptr, world)
+    bounds = W.partition_rows(row_ptr, world, args.row_weight)
     r0, r1 = bounds[rank], bounds[rank + 1]
     mine = full.rows(r0, r1)
     if world > 1:
@@ -559,10 +580,15 @@ def main():
     del lhs, out
 
     # ---- end to end: host buffers in, host result out, every step -----------------------------
+    # Host side of the job: every rank holds its CSR slice and, at N > 1, 1/N of the dense
+    # operand's rows in pinned memory; the operand is assembled on the GPUs by one all-gather
+    # over NVLink per step instead of N full copies over PCIe.
     h_rp, h_col, h_val = (t.cpu().pin_memory() for t in (mine.row_ptr, mine.col, mine.val))
-    h_X = X.cpu().pin_memory()
+    shard = n_vert // world
+    h_X = X[rank * shard:(rank + 1) * shard].cpu().pin_memory() if world > 1 else X.cpu().pin_memory()
     h_C = torch.empty((my_rows, N_DENSE), dtype=torch.float32).pin_memory()
     d_rp, d_col, d_val, d_X = (torch.empty_like(t) for t in (mine.row_ptr, mine.col, mine.val, X))
+    d_shard = torch.empty((shard, N_DENSE), dtype=torch.float32, device=dev) if world > 1 else None
     h2d = sum(t.numel() * t.element_size() for t in (h_rp, h_col, h_val, h_X))
     d2h = h_C.numel() * 4
 
@@ -570,7 +596,11 @@ def main():
         d_rp.copy_(h_rp, non_blocking=True)
         d_col.copy_(h_col, non_blocking=True)
         d_val.copy_(h_val, non_blocking=True)
-        d_X.copy_(h_X, non_blocking=True)
+        if world > 1:
+            d_shard.copy_(h_X, non_blocking=True)
+            dist.all_gather_into_tensor(d_X, d_shard)
+        else:
+            d_X.copy_(h_X, non_blocking=True)
         m = capi.preprocess(d_rp, my_nnz, 512, 32, 4)   # device-side row decomposition (reads 2 counts back)
         C.zero_()                                        # the API's contract: C arrives zero-filled
 
@@ -592,7 +622,11 @@ def main():
     ms_e2e = max_over_ranks(a.elapsed_time(b) / args.e2e_steps)
     e2e = {"value": 2.0 * nnz * N_DENSE / ms_e2e / 1e6, "unit": "GFLOP/s", "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
-           "includes": "H2D of CSR + dense operand from pinned memory, device preprocessing, C zero-fill, SpMM, D2H of C"}
+           "includes": ("H2D of the rank's CSR slice + dense operand from pinned memory, device preprocessing, "
+                        "C zero-fill, SpMM, D2H of the rank's C rows" if world == 1 else
+                        "per rank: H2D of its CSR slice + 1/N of the dense operand from pinned memory, NCCL "
+                        "all-gather of the operand, device preprocessing, C zero-fill, SpMM, D2H of its C rows; "
+                        "bytes are rank 0's")}
     checksum = float(h_C.double().sum())
 
     # ---- CPU baseline (rank 0, single-GPU run only) ----------------------------------------------
@@ -630,7 +664,9 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"rmat{args.scale}_spmm_n{N_DENSE}", "rows": n_vert, "nnz": nnz, "n": N_DENSE,
-                       "partition": f"nnz-balanced contiguous rows over {world} rank(s)",
+                       "partition": (f"nnz-balanced contiguous rows over {world} rank(s)" if not args.row_weight else
+                                     f"contiguous rows over {world} rank(s), cost nnz + {args.row_weight}*rows"),
+                       "rank0_rows": my_rows, "rank0_nnz": my_nnz,
                        "l2": "inputs larger than L2 (dense operand 4.3 GB, CSR 1 GB); no flush between steps",
                        "m1_rank0": meta.m1, "m2_rank0": meta.m2},
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps, "nnz_per_s": nnz / ms_step * 1e3,
@@ -639,7 +675,7 @@ def main():
         }
         if configs is not None:
             line["configs"] = configs
-        print(json.dumps(line))
+        console.emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 

@@ -184,14 +184,25 @@ def rmat(scale: int = 23, edge_factor: int = 16, a: float = 0.57, b: float = 0.1
 
 
 # ---------------------------------------------------------------------------------------
-def partition_rows(row_ptr: torch.Tensor, parts: int):
-    """nnz-balanced contiguous row ranges: cut p lies at the first row whose offset reaches
-    nnz * p / parts.  Returns ``parts + 1`` row indices (first 0, last M)."""
-    rp = row_ptr.to(torch.int64).cpu()
+def partition_rows(row_ptr: torch.Tensor, parts: int, row_weight: float = 0.0):
+    """Contiguous row ranges of equal cost, cost(row) = nnz(row) + row_weight.
+
+    row_weight = 0 is the plain nnz-balanced partition: cut p lies at the first row whose
+    offset reaches nnz * p / parts.  A positive row_weight also counts the per-row work
+    (one row of the result is written per sparse row, as costly as gathering one dense row
+    for a nonzero), which matters when the ranges differ a lot in their number of rows.
+    Returns ``parts + 1`` row indices (first 0, last M)."""
+    rp = row_ptr.to(torch.float64).cpu() if row_weight else row_ptr.to(torch.int64).cpu()
     m = rp.numel() - 1
-    nnz = int(rp[-1])
-    targets = torch.tensor([(nnz * p) // parts for p in range(1, parts)], dtype=torch.int64)
-    cuts = torch.searchsorted(rp, targets, right=False).clamp(0, m).tolist() if parts > 1 else []
+    if row_weight:
+        cost = rp + row_weight * torch.arange(m + 1, dtype=torch.float64)
+        total = float(cost[-1])
+        targets = torch.tensor([total * p / parts for p in range(1, parts)], dtype=torch.float64)
+    else:
+        cost = rp
+        nnz = int(rp[-1])
+        targets = torch.tensor([(nnz * p) // parts for p in range(1, parts)], dtype=torch.int64)
+    cuts = torch.searchsorted(cost, targets, right=False).clamp(0, m).tolist() if parts > 1 else []
     bounds = [0] + [int(c) for c in cuts] + [m]
     for i in range(1, len(bounds)):
         bounds[i] = max(bounds[i], bounds[i - 1])
