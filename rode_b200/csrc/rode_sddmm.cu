@@ -2,32 +2,32 @@
 //
 // Stands in for the reference's SDDMMKernel4Block / SDDMMKernel4Residue
 // (RoDe_SDDMM/RoDeSddmm.cu:15-203, :206-494) and their launchers (:496-545).  The work
-// split follows the reference's metadata (block segments, residue rows); inside a unit:
+// split follows the reference's metadata (block segments, residue rows); one kernel,
+// sddmm_items, serves both lists and every K:
 //
-//  * A dense row of length K is covered by L = K/4 lanes, one LDG.128 per lane, so a gather
-//    of rhs[col, :] is one coalesced request of 4*K bytes.  K = 32, 64, 128 -> L = 8, 16, 32;
-//    a warp holds G = 32/L lane groups.
-//  * Nonzeros are handled in chunks of 32 (lane t fetches column and value of nonzero t,
-//    two chunks ahead) and, inside a chunk, in batches of 8 per lane group: 8 independent
-//    LDG.128 per lane, one partial dot product (this lane's 4 of the K terms) per nonzero,
-//    then a shuffle reduce that halves the number of live partials at every step
-//    (4 + 2 + 1 exchanges, then a butterfly over the remaining lanes): ~1.2 shuffles per
-//    nonzero and only 8 partials in registers.  The finished dot products are handed to
-//    the lanes that hold the matching values, so results are stored coalesced.
-//  * sddmm_block (K = 32, 64; segments of up to 512 nonzeros): one warp per block segment;
-//    the lhs row slice stays in registers.  The last segment of a row also produces the
-//    row's tail (shorter than 32) that the reference leaves to its residue kernel.
-//    sddmm_rows (K = 32, 64): one lane group per residue row without a block part.
-//  * sddmm_stream (K = 128, where segments are only 32 long): a warp takes 32 consecutive
-//    items (segments, or residue rows without a block part): lane j reads the descriptor of
-//    item j, and the nonzeros of the 32 items run through the gather as one stream, the
-//    lhs row being switched (and the next one prefetched) where the stream crosses into the
-//    next item.  The dependent chain row index -> row pointer -> column -> dense row is
-//    paid once per 32 items.
-//  * CTAs are one or two warps: a CTA's slot is held until its slowest warp finishes.
+//  * A warp takes up to 32 consecutive ITEMS (block segments, or residue rows that have no
+//    block part): lane j reads the descriptor of item j, so the dependent chain row index ->
+//    row pointer -> column -> dense row is paid once per 32 items.  The nonzeros of the items,
+//    concatenated, form one entry stream.  The last segment of a row also covers the row's
+//    tail (shorter than 32) that the reference leaves to its residue kernel.
+//  * A dense row of length K is covered by a lane group of L lanes, VPL 16-byte loads per
+//    lane (K = 4 * L * VPL).  The G = 32/L groups of the warp split the stream into G equal
+//    contiguous parts (equal in nonzeros, not in items), so all groups run the same number of
+//    iterations and a group walks through its items in order; it keeps the lhs row slice of
+//    its current item in registers and prefetches the next item's.
+//  * Nonzeros are handled in chunks of L per group (lane l fetches column and value of
+//    nonzero l, two chunks ahead) and, inside a chunk, in batches of 8: 8 * VPL independent
+//    LDG.128 per lane, one partial dot product per nonzero, then a shuffle reduce that halves
+//    the number of live partials at every step (4 + 2 + 1 exchanges, then a butterfly over
+//    the remaining lanes).  The finished dot products land in the lanes that hold the
+//    matching values, so results are stored coalesced.
+//  * sddmm_block: where segments are long (K = 32, 64: up to 543 nonzeros) a segment gets a
+//    warp of its own; chunk loads are then plain coalesced loads without any search and the
+//    lhs slice never changes (power-law K = 32: 370 us against 744 us through sddmm_items).
+//  * One-warp CTAs: a CTA's slot is held until its slowest warp finishes.
 //
 // Per nonzero: 12 B of CSR data/output plus 4*K bytes of rhs (L1/L2/HBM by reuse); per item
-// 4*K bytes of lhs.  No shared memory, no atomics, no workspace.
+// 4*K bytes of lhs per group that touches it.  No atomics, no workspace.
 #include <climits>
 
 #include "rode_common.cuh"
@@ -35,20 +35,27 @@
 namespace rode {
 namespace {
 
-#ifndef RODE_SDDMM_CTA_WARPS
-#define RODE_SDDMM_CTA_WARPS 1
+// Lanes per dense row for K = 32 / 64 / 128; with fewer lanes the rest of the row is covered
+// by several 16-byte loads per lane (VPL > 1).  Measured on B200: VPL = 2 costs 123 registers
+// and is slower than one load per lane (R-MAT-21 K = 64: 1.18 ms against 1.02 ms; power-law
+// K = 128: 2.64 ms against 2.39 ms), so the defaults keep VPL = 1.
+#ifndef RODE_SDDMM_L32
+#define RODE_SDDMM_L32 8
 #endif
-#ifndef RODE_SDDMM_ROWS_CTA
-#define RODE_SDDMM_ROWS_CTA 64
+#ifndef RODE_SDDMM_L64
+#define RODE_SDDMM_L64 16
 #endif
-constexpr int kCtaWarps = RODE_SDDMM_CTA_WARPS;
-constexpr int kCtaThreads = 32 * kCtaWarps;
-constexpr int kRowsCtaThreads = RODE_SDDMM_ROWS_CTA;
-constexpr int kBatch = 8;  // nonzeros per lane group per batch = LDG.128 in flight per lane
+#ifndef RODE_SDDMM_L128
+#define RODE_SDDMM_L128 32
+#endif
+#ifndef RODE_SDDMM_LONG_SEGMENTS_BY_WARP
+#define RODE_SDDMM_LONG_SEGMENTS_BY_WARP 1
+#endif
+constexpr int kBatch = 8;  // nonzeros per lane group per batch
 constexpr unsigned kFull = 0xffffffffu;
 
-__device__ __forceinline__ float dot4(const float4 &a, const float4 &b) {
-    return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, a.x * b.x)));
+__device__ __forceinline__ float dot4(const float4 &a, const float4 &b, float acc) {
+    return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, acc))));
 }
 
 // p[u] = this lane's share of the dot product of nonzero u of the batch (u = 0..7).
@@ -70,6 +77,168 @@ __device__ __forceinline__ float reduce_batch(float (&p)[kBatch], int l, unsigne
 #pragma unroll
     for (int w = L / 16; w >= 1; w >>= 1) r += __shfl_xor_sync(gmask, r, w, L);
     return r;
+}
+
+// kSegments: items are block segments (block_r_ind / st_off); otherwise residue rows
+// (residue_r_ind) without a block part.
+template <int L, int VPL, bool kSegments>
+__global__ void __launch_bounds__(32)
+sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, const int *__restrict__ st_off,
+            const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
+            const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,
+            float *__restrict__ out) {
+    constexpr int G = 32 / L;
+    constexpr size_t kRowVecs = L * VPL;  // float4 per dense row (K / 4)
+    constexpr int kAlign = 4;             // vec_len of the preprocessing
+    constexpr int kBlockK = 32;           // k_block of the preprocessing
+    __shared__ int s_end[32];             // stream position where item j ends
+    __shared__ int s_row[32];             // row of item j
+    const int lane = threadIdx.x;
+    const int g = lane / L, l = lane % L;
+    const unsigned gmask = group_mask<L>(lane);
+    const long long item0 = static_cast<long long>(blockIdx.x) * items_per_warp;
+    if (item0 >= n_items) return;
+
+    // ---- descriptors: lane j owns item item0 + j --------------------------------------------
+    int row = 0, begin = 0, len = 0;
+    if (lane < items_per_warp && item0 + lane < n_items) {
+        const int item = static_cast<int>(item0) + lane;
+        row = __ldg(item_rows + item);
+        if (kSegments) {
+            begin = __ldg(st_off + item);
+            const int next = (item + 1 < n_items) ? __ldg(st_off + item + 1) : INT_MAX;
+            len = min(__ldg(row_offsets + row + 1), next) - begin;
+        } else {
+            begin = __ldg(row_offsets + row);
+            const int end = __ldg(row_offsets + row + 1);
+            if (end - begin + (begin % kAlign) < kBlockK) len = end - begin;
+        }
+    }
+    int start = len;  // exclusive prefix sum of len
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(kFull, start, d);
+        if (lane >= d) start += up;
+    }
+    const int total = __shfl_sync(kFull, start, 31);
+    s_end[lane] = start;  // inclusive sum = end position
+    s_row[lane] = row;
+    start -= len;
+    const unsigned nonempty = __ballot_sync(kFull, len > 0);
+    if (total == 0) return;
+    __syncwarp();
+
+    // ---- this group's contiguous part of the stream: [p0, p1) ----------------------------------
+    const int per = (((total + G - 1) / G) + kBatch - 1) & ~(kBatch - 1);
+    const int p0 = g * per;
+    const int p1 = min(p0 + per, total);
+    const int n_chunks = (per + L - 1) / L;  // same for every group
+
+    // stream position p -> (nonzero index, column, value); every lane of the warp calls
+    auto fetch = [&](int p, int &e, int &c, float &v) {
+        int lo = 0;
+#pragma unroll
+        for (int step = 16; step >= 1; step >>= 1) {
+            const int s = __shfl_sync(kFull, start, lo + step);
+            if (s <= p) lo += step;
+        }
+        const int b0 = __shfl_sync(kFull, begin, lo);
+        const int s0 = __shfl_sync(kFull, start, lo);
+        e = -1;
+        c = 0;
+        v = 0.f;
+        if (p < p1) {
+            e = b0 + (p - s0);
+            c = ld_stream(column_indices + e);
+            v = ld_stream(values + e);
+        }
+    };
+
+    const float4 *lhs_lane = reinterpret_cast<const float4 *>(lhs) + l;
+    const float4 *rhs_lane = reinterpret_cast<const float4 *>(rhs) + l;
+
+    // ---- item the group is in, its lhs slice, and the next item's (prefetched) --------------------
+    // first item whose end lies beyond p0 = number of items that end at or before p0
+    int cur = 0;
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg) {
+        const int cnt = __popc(__ballot_sync(kFull, s_end[lane] <= gg * per));
+        if (g == gg) cur = cnt;
+    }
+    cur = min(cur, 31);
+    auto next_nonempty = [&](int after) {  // first non-empty item with index > after, or -1
+        const unsigned rest = (after >= 31) ? 0u : (nonempty & (kFull << (after + 1)));
+        return __ffs(rest) - 1;
+    };
+    int cur_end = s_end[cur];
+    int nxt = next_nonempty(cur);
+    float4 a_cur[VPL], a_nxt[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+        a_cur[v] = __ldg(lhs_lane + static_cast<size_t>(s_row[cur]) * kRowVecs + v * L);
+        a_nxt[v] = a_cur[v];
+        if (nxt >= 0) a_nxt[v] = __ldg(lhs_lane + static_cast<size_t>(s_row[nxt]) * kRowVecs + v * L);
+    }
+
+    int e_cur, c_cur, e_nxt, c_nxt;
+    float v_cur, v_nxt;
+    fetch(p0 + l, e_cur, c_cur, v_cur);
+    fetch(p0 + L + l, e_nxt, c_nxt, v_nxt);
+    int pos = p0;  // stream position of the next nonzero this group multiplies
+    for (int ch = 0; ch < n_chunks; ++ch) {
+        int e_pre, c_pre;
+        float v_pre;
+        fetch(p0 + (ch + 2) * L + l, e_pre, c_pre, v_pre);
+        const int cnt = min(L, p1 - (p0 + ch * L));  // valid nonzeros of this chunk (may be <= 0)
+        float mine = 0.f;
+#pragma unroll
+        for (int b = 0; b < L / kBatch; ++b) {
+            if (b * kBatch < cnt) {  // uniform inside the group; no warp-wide shuffles inside
+                float4 bb[kBatch][VPL];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const int t = b * kBatch + u;
+                    const int cc = __shfl_sync(gmask, c_cur, t, L);
+#pragma unroll
+                    for (int v = 0; v < VPL; ++v) {
+                        bb[u][v] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (t < cnt) bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc) * kRowVecs + v * L);
+                    }
+                }
+                float p[kBatch];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    if (pos == cur_end && nxt >= 0) {  // the group enters its next item
+                        cur = nxt;
+                        cur_end = s_end[cur];
+                        nxt = next_nonempty(cur);
+#pragma unroll
+                        for (int v = 0; v < VPL; ++v) {
+                            a_cur[v] = a_nxt[v];
+                            if (nxt >= 0)
+                                a_nxt[v] = __ldg(lhs_lane + static_cast<size_t>(s_row[nxt]) * kRowVecs + v * L);
+                        }
+                    }
+                    float d = 0.f;
+#pragma unroll
+                    for (int v = 0; v < VPL; ++v) d = dot4(a_cur[v], bb[u][v], d);
+                    p[u] = d;
+                    ++pos;
+                }
+                const float r = reduce_batch<L>(p, l, gmask);
+                // nonzero u of the batch sits in lanes u * (L/8) ..; lane b*8 + u of the group wants it
+                const float got = (L == kBatch) ? r : __shfl_sync(gmask, r, (l & (kBatch - 1)) * (L / kBatch), L);
+                if ((l / kBatch) == b) mine = got;
+            }
+        }
+        if (e_cur >= 0) st_stream(out + e_cur, v_cur * mine);
+        e_cur = e_nxt;
+        c_cur = c_nxt;
+        v_cur = v_nxt;
+        e_nxt = e_pre;
+        c_nxt = c_pre;
+        v_nxt = v_pre;
+    }
 }
 
 // Dot products of one chunk.  Lane t of the warp holds column `c` of nonzero t; `cnt`
@@ -95,7 +264,7 @@ __device__ __forceinline__ float chunk_dots(const float4 &a, int c, int cnt, con
         }
         float p[kBatch];
 #pragma unroll
-        for (int u = 0; u < kBatch; ++u) p[u] = dot4(a, bb[u]);
+        for (int u = 0; u < kBatch; ++u) p[u] = dot4(a, bb[u], 0.f);
         const float r = reduce_batch<L>(p, l, gmask);
         // nonzero u of the batch sits in lanes u * (L/8) ..; lane b*8 + u of the group wants it
         const float got = __shfl_sync(gmask, r, (l & (kBatch - 1)) * (L / kBatch), L);
@@ -105,13 +274,16 @@ __device__ __forceinline__ float chunk_dots(const float4 &a, int c, int cnt, con
 }
 
 // ---------------------------------------------------------------------------------------
+// One warp per block segment (used where segments are long, K = 32 and 64: up to 543
+// nonzeros): coalesced chunk loads without any search, the G groups take consecutive
+// L-nonzero pieces of each 32-nonzero chunk, the lhs slice stays in registers.
 template <int L>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(32)
 sddmm_block(int m1, int k, const int *__restrict__ block_r_ind, const int *__restrict__ st_off,
             const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
             const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,
             float *__restrict__ out) {
-    const int seg = blockIdx.x * kCtaWarps + (threadIdx.x >> 5);
+    const int seg = blockIdx.x;
     if (seg >= m1) return;
     const int lane = threadIdx.x & 31;
     const int l = lane % L;
@@ -151,218 +323,47 @@ sddmm_block(int m1, int k, const int *__restrict__ block_r_ind, const int *__res
     }
 }
 
-// One lane group per residue row without a block part.
-template <int L>
-__global__ void __launch_bounds__(kRowsCtaThreads)
-sddmm_rows(int m2, int k, const int *__restrict__ residue_r_ind, const int *__restrict__ row_offsets,
-           const int *__restrict__ column_indices, const float *__restrict__ values,
-           const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out) {
-    constexpr int kAlign = 4;    // vec_len of the preprocessing
-    constexpr int kBlockK = 32;  // k_block of the preprocessing
-    const int item = (blockIdx.x * kRowsCtaThreads + threadIdx.x) / L;
-    if (item >= m2) return;
-    const int lane = threadIdx.x & 31;
-    const int l = lane % L;
-    const unsigned gmask = group_mask<L>(lane);
-
-    const int row = __ldg(residue_r_ind + item);
-    const int begin = __ldg(row_offsets + row);
-    const int end = __ldg(row_offsets + row + 1);
-    // Aligned length >= k_block: the row has a block part whose last segment produced the tail.
-    if (end - begin + (begin % kAlign) >= kBlockK || end == begin) return;
-
-    const size_t row_vecs = static_cast<size_t>(k) / 4;
-    const float4 a = __ldg(reinterpret_cast<const float4 *>(lhs) + static_cast<size_t>(row) * row_vecs + l);
-    const float4 *rhs_lane = reinterpret_cast<const float4 *>(rhs) + l;
-
-    for (int base = begin; base < end; base += L) {
-        const int e = base + l;
-        int c = 0;
-        float v = 0.f;
-        if (e < end) {
-            c = ld_stream(column_indices + e);
-            v = ld_stream(values + e);
-        }
-        const int cnt = min(L, end - base);
-        float mine = 0.f;
-#pragma unroll
-        for (int b = 0; b < L / kBatch; ++b) {
-            if (b * kBatch >= cnt) break;
-            float4 bb[kBatch];
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int t = b * kBatch + u;
-                const int cc = __shfl_sync(gmask, c, t, L);
-                bb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (t < cnt) bb[u] = ld_dense(rhs_lane + static_cast<size_t>(cc) * row_vecs);
-            }
-            float p[kBatch];
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) p[u] = dot4(a, bb[u]);
-            const float r = reduce_batch<L>(p, l, gmask);
-            const float got = __shfl_sync(gmask, r, (l & (kBatch - 1)) * (L / kBatch), L);
-            if ((l / kBatch) == b) mine = got;
-        }
-        if (e < end) st_stream(out + e, v * mine);
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cached[dev] = v;
     }
+    return cached[dev];
 }
 
-// ---------------------------------------------------------------------------------------
-// K = 128: a warp streams the nonzeros of 32 consecutive items.  kSegments: items are block
-// segments (block_r_ind / st_off); otherwise residue rows (residue_r_ind) without block part.
-template <bool kSegments>
-__global__ void __launch_bounds__(32)
-sddmm_stream(int n_items, const int *__restrict__ item_rows, const int *__restrict__ st_off,
-             const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
-             const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,
-             float *__restrict__ out) {
-    constexpr int L = 32;
-    constexpr int kAlign = 4;
-    constexpr int kBlockK = 32;
-    constexpr size_t kRowVecs = 32;  // K / 4
-    const int lane = threadIdx.x;
-    const long long item0 = static_cast<long long>(blockIdx.x) * 32;
-    if (item0 >= n_items) return;
-
-    // ---- descriptors: lane j owns item item0 + j ----------------------------------------
-    int row = 0, begin = 0, len = 0;
-    if (item0 + lane < n_items) {
-        const int item = static_cast<int>(item0) + lane;
-        row = __ldg(item_rows + item);
-        if (kSegments) {
-            begin = __ldg(st_off + item);
-            const int next = (item + 1 < n_items) ? __ldg(st_off + item + 1) : INT_MAX;
-            len = min(__ldg(row_offsets + row + 1), next) - begin;
-        } else {
-            begin = __ldg(row_offsets + row);
-            const int end = __ldg(row_offsets + row + 1);
-            if (end - begin + (begin % kAlign) < kBlockK) len = end - begin;
-        }
-    }
-    int start = len;  // exclusive prefix sum of len
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const int up = __shfl_up_sync(kFull, start, d);
-        if (lane >= d) start += up;
-    }
-    const int total = __shfl_sync(kFull, start, 31);
-    start -= len;
-    unsigned todo = __ballot_sync(kFull, len > 0);
-    if (todo == 0) return;
-
-    // stream position p -> (nonzero index, column, value); all lanes call
-    auto fetch = [&](int p, int &e, int &c, float &v) {
-        int lo = 0;
-#pragma unroll
-        for (int step = 16; step >= 1; step >>= 1) {
-            const int s = __shfl_sync(kFull, start, lo + step);
-            if (s <= p) lo += step;
-        }
-        const int b0 = __shfl_sync(kFull, begin, lo);
-        const int s0 = __shfl_sync(kFull, start, lo);
-        e = -1;
-        c = 0;
-        v = 0.f;
-        if (p < total) {
-            e = b0 + (p - s0);
-            c = ld_stream(column_indices + e);
-            v = ld_stream(values + e);
-        }
-    };
-
-    const float4 *lhs_lane = reinterpret_cast<const float4 *>(lhs) + lane;
-    const float4 *rhs_lane = reinterpret_cast<const float4 *>(rhs) + lane;
-
-    // consumer state: item being processed, its lhs slice, and the next item's (prefetched)
-    int cur = __ffs(todo) - 1;
-    todo &= todo - 1;
-    int cur_end = __shfl_sync(kFull, start, cur) + __shfl_sync(kFull, len, cur);
-    float4 a_cur = __ldg(lhs_lane + static_cast<size_t>(__shfl_sync(kFull, row, cur)) * kRowVecs);
-    float4 a_nxt = a_cur;
-    if (todo) a_nxt = __ldg(lhs_lane + static_cast<size_t>(__shfl_sync(kFull, row, __ffs(todo) - 1)) * kRowVecs);
-    int pos = 0;
-
-    int e_cur, c_cur, e_nxt, c_nxt;
-    float v_cur, v_nxt;
-    fetch(lane, e_cur, c_cur, v_cur);
-    fetch(32 + lane, e_nxt, c_nxt, v_nxt);
-    for (int base = 0; base < total; base += 32) {
-        const int cnt = min(32, total - base);
-        int e_pre, c_pre;
-        float v_pre;
-        fetch(base + 64 + lane, e_pre, c_pre, v_pre);
-        float mine = 0.f;
-#pragma unroll
-        for (int b = 0; b < L / kBatch; ++b) {
-            if (b * kBatch >= cnt) break;
-            float4 bb[kBatch];
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int t = b * kBatch + u;
-                const int cc = __shfl_sync(kFull, c_cur, t);
-                bb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (t < cnt) bb[u] = ld_dense(rhs_lane + static_cast<size_t>(cc) * kRowVecs);
-            }
-            float p[kBatch];
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                if (pos == cur_end) {  // the stream enters the next item: switch the lhs row
-                    cur = __ffs(todo) - 1;
-                    todo &= todo - 1;
-                    cur_end = (cur >= 0) ? __shfl_sync(kFull, start, cur & 31) + __shfl_sync(kFull, len, cur & 31)
-                                         : INT_MAX;
-                    a_cur = a_nxt;
-                    if (todo)
-                        a_nxt = __ldg(lhs_lane +
-                                      static_cast<size_t>(__shfl_sync(kFull, row, __ffs(todo) - 1)) * kRowVecs);
-                }
-                p[u] = dot4(a_cur, bb[u]);
-                ++pos;
-            }
-            const float r = reduce_batch<L>(p, lane, kFull);
-            const float got = __shfl_sync(kFull, r, (lane & (kBatch - 1)) * (L / kBatch));
-            if ((lane / kBatch) == b) mine = got;
-        }
-        if (e_cur >= 0) st_stream(out + e_cur, v_cur * mine);
-        e_cur = e_nxt;
-        c_cur = c_nxt;
-        v_cur = v_nxt;
-        e_nxt = e_pre;
-        c_nxt = c_pre;
-        v_nxt = v_pre;
-    }
+// Items per warp: 32 when that still gives every SM several waves of warps, fewer otherwise.
+int items_per_warp(int n_items, int cap) {
+    const long long slots = 4LL * 24 * sm_count();
+    long long per = (n_items + slots - 1) / slots;
+    per = per < 1 ? 1 : (per > cap ? cap : per);
+    return static_cast<int>(per);
 }
 
-template <int L>
-int launch_k(int m1, int m2, int k, const int *block_r_ind, const int *residue_r_ind, const int *st_off,
+template <int L, int VPL>
+int launch_k(int m1, int m2, int seg_cap, const int *block_r_ind, const int *residue_r_ind, const int *st_off,
              const int *row_offsets, const int *col, const float *values, const float *lhs, const float *rhs,
              float *out, cudaStream_t s1, cudaStream_t s2) {
     if (m1 > 0) {
-        sddmm_block<L><<<(m1 + kCtaWarps - 1) / kCtaWarps, kCtaThreads, 0, s1>>>(
-            m1, k, block_r_ind, st_off, row_offsets, col, values, lhs, rhs, out);
-        RODE_CHECK_LAUNCH("rode::sddmm_block");
+        if (VPL == 1 && seg_cap < 32 && RODE_SDDMM_LONG_SEGMENTS_BY_WARP) {
+            sddmm_block<L><<<m1, 32, 0, s1>>>(m1, 4 * L, block_r_ind, st_off, row_offsets, col, values, lhs, rhs,
+                                              out);
+            RODE_CHECK_LAUNCH("rode::sddmm_block");
+        } else {
+            const int per = items_per_warp(m1, seg_cap);
+            sddmm_items<L, VPL, true><<<(m1 + per - 1) / per, 32, 0, s1>>>(m1, per, block_r_ind, st_off,
+                                                                            row_offsets, col, values, lhs, rhs, out);
+            RODE_CHECK_LAUNCH("rode::sddmm_items<segments>");
+        }
     }
     if (m2 > 0) {
-        constexpr int kRowsPerCta = kRowsCtaThreads / L;
-        sddmm_rows<L><<<(m2 + kRowsPerCta - 1) / kRowsPerCta, kRowsCtaThreads, 0, s2>>>(
-            m2, k, residue_r_ind, row_offsets, col, values, lhs, rhs, out);
-        RODE_CHECK_LAUNCH("rode::sddmm_rows");
-    }
-    return RODE_OK;
-}
-
-int launch_k128(int m1, int m2, const int *block_r_ind, const int *residue_r_ind, const int *st_off,
-                const int *row_offsets, const int *col, const float *values, const float *lhs, const float *rhs,
-                float *out, cudaStream_t s1, cudaStream_t s2) {
-    if (m1 > 0) {
-        sddmm_stream<true><<<(m1 + 31) / 32, 32, 0, s1>>>(m1, block_r_ind, st_off, row_offsets, col, values, lhs,
-                                                          rhs, out);
-        RODE_CHECK_LAUNCH("rode::sddmm_stream<segments>");
-    }
-    if (m2 > 0) {
-        sddmm_stream<false><<<(m2 + 31) / 32, 32, 0, s2>>>(m2, residue_r_ind, nullptr, row_offsets, col, values,
-                                                           lhs, rhs, out);
-        RODE_CHECK_LAUNCH("rode::sddmm_stream<rows>");
+        const int per = items_per_warp(m2, 32);
+        sddmm_items<L, VPL, false><<<(m2 + per - 1) / per, 32, 0, s2>>>(m2, per, residue_r_ind, nullptr,
+                                                                         row_offsets, col, values, lhs, rhs, out);
+        RODE_CHECK_LAUNCH("rode::sddmm_items<rows>");
     }
     return RODE_OK;
 }
@@ -387,14 +388,18 @@ extern "C" int rode_sddmm_f32(int m1, int m2, int n, int k, const int *block_r_i
     if (!aligned_to(lhs, 16) || !aligned_to(rhs, 16))
         return fail(RODE_ERR_INVALID_ARGUMENT, "sddmm: lhs and rhs must be 16-byte aligned");
     switch (k) {
+        // (L, VPL) with K = 4 * L * VPL; segments per warp: few when segments are long (512)
         case 32:
-            return launch_k<8>(m1, m2, k, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values,
-                               lhs, rhs, out, stream1, stream2);
+            return launch_k<RODE_SDDMM_L32, 8 / RODE_SDDMM_L32>(m1, m2, 4, block_r_ind, residue_r_ind, st_off,
+                                                                 row_offsets, column_indices, values, lhs, rhs, out,
+                                                                 stream1, stream2);
         case 64:
-            return launch_k<16>(m1, m2, k, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices,
-                                values, lhs, rhs, out, stream1, stream2);
+            return launch_k<RODE_SDDMM_L64, 16 / RODE_SDDMM_L64>(m1, m2, 4, block_r_ind, residue_r_ind, st_off,
+                                                                  row_offsets, column_indices, values, lhs, rhs, out,
+                                                                  stream1, stream2);
         default:
-            return launch_k128(m1, m2, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values,
-                               lhs, rhs, out, stream1, stream2);
+            return launch_k<RODE_SDDMM_L128, 32 / RODE_SDDMM_L128>(m1, m2, 32, block_r_ind, residue_r_ind, st_off,
+                                                                    row_offsets, column_indices, values, lhs, rhs,
+                                                                    out, stream1, stream2);
     }
 }
