@@ -139,6 +139,10 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
         c_nxt = c_pre;
         v_nxt = v_pre;
     }
+    // Programmatic dependent launch: once every warp of this grid is past its gathers, the
+    // fix-up grid may be scheduled and run its prologue (it still waits for this grid's
+    // completion before it reads the workspace).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
     for (int w = L; w < 32; w <<= 1) vadd(acc, vshfl_xor(kFull, acc, w));
 
@@ -185,6 +189,9 @@ spmm_fixup(int m1, int n, const int *__restrict__ row_offsets, const int *__rest
         }
     }
     unsigned todo = __ballot_sync(kFull, head);
+    // Everything above read only the caller's metadata; the workspace is written by the
+    // preceding spmm_block grid: wait for it (no-op when launched without the attribute).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     while (todo) {
         const int src = __ffs(todo) - 1;
         todo &= todo - 1;
@@ -462,8 +469,21 @@ int launch_width(int m1, int m2, int n, const T *values, const int *col, const i
             spmm_block<T, L, Batch<L>::kRows><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets,
                                                                             block_r_ind, st_off, B, C, partial);
         RODE_CHECK_LAUNCH("rode::spmm_block");
-        spmm_fixup<T><<<(m1 + kFixupThreads - 1) / kFixupThreads, kFixupThreads, 0, s1>>>(
-            m1, n, row_offsets, block_r_ind, st_off, partial, C);
+        // fix-up as a programmatic dependent of spmm_block: its launch latency and its
+        // metadata prologue overlap the tail of the block grid
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((m1 + kFixupThreads - 1) / kFixupThreads);
+        cfg.blockDim = dim3(kFixupThreads);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = s1;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const T *partial_in = partial;
+        RODE_CUDA_TRY(cudaLaunchKernelEx(&cfg, spmm_fixup<T>, m1, n, row_offsets, block_r_ind, st_off, partial_in,
+                                         C));
         RODE_CHECK_LAUNCH("rode::spmm_fixup");
     }
     if (m2 > 0) {
