@@ -53,7 +53,7 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--scale", type=int, default=23, help="R-MAT scale of the headline workload")
     p.add_argument("--no-extra", action="store_true", help="skip the secondary configs and the CPU baseline")
-    p.add_argument("--e2e-steps", type=int, default=3)
+    p.add_argument("--e2e-steps", type=int, default=6)
     p.add_argument("--row-weight", type=float, default=1.0,
                    help="multi-GPU partition: cost of a row = its nnz + this (0 = plain nnz-balanced)")
     p.add_argument("--only", choices=["spmm", "sddmm"], default=None,
@@ -587,46 +587,80 @@ def main():
     shard = n_vert // world
     h_X = X[rank * shard:(rank + 1) * shard].cpu().pin_memory() if world > 1 else X.cpu().pin_memory()
     h_C = torch.empty((my_rows, N_DENSE), dtype=torch.float32).pin_memory()
-    d_rp, d_col, d_val, d_X = (torch.empty_like(t) for t in (mine.row_ptr, mine.col, mine.val, X))
-    d_shard = torch.empty((shard, N_DENSE), dtype=torch.float32, device=dev) if world > 1 else None
     h2d = sum(t.numel() * t.element_size() for t in (h_rp, h_col, h_val, h_X))
     d2h = h_C.numel() * 4
+    # Software pipeline over steps: two sets of device input buffers and two result buffers,
+    # one copy-in stream, the compute streams, one copy-out stream.  Step i+1's H2D runs while
+    # step i computes and step i's result goes back (PCIe is full duplex).
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    bufs = []
+    for _ in range(2):
+        bufs.append({
+            "rp": torch.empty_like(mine.row_ptr), "col": torch.empty_like(mine.col), "val": torch.empty_like(mine.val),
+            "X": (torch.empty((shard, N_DENSE), dtype=torch.float32, device=dev) if world > 1 else torch.empty_like(X)),
+            "C": torch.empty((my_rows, N_DENSE), dtype=torch.float32, device=dev),
+            "in_ready": torch.cuda.Event(), "in_free": torch.cuda.Event(), "out_ready": torch.cuda.Event(),
+            "out_free": torch.cuda.Event(),
+        })
+    d_X_full = torch.empty_like(X) if world > 1 else None
+    del C
 
-    def e2e_step():
-        d_rp.copy_(h_rp, non_blocking=True)
-        d_col.copy_(h_col, non_blocking=True)
-        d_val.copy_(h_val, non_blocking=True)
+    def copy_in(i):
+        bf = bufs[i % 2]
+        s_in.wait_event(bf["in_free"])          # the compute of step i-2 is done with this set
+        with torch.cuda.stream(s_in):
+            bf["rp"].copy_(h_rp, non_blocking=True)
+            bf["col"].copy_(h_col, non_blocking=True)
+            bf["val"].copy_(h_val, non_blocking=True)
+            bf["X"].copy_(h_X, non_blocking=True)
+            bf["in_ready"].record(s_in)
+
+    def compute_and_copy_out(i):
+        bf = bufs[i % 2]
+        fj.cur.wait_event(bf["in_ready"])
+        fj.cur.wait_event(bf["out_free"])       # the D2H of step i-2 is done with this C
         if world > 1:
-            d_shard.copy_(h_X, non_blocking=True)
-            dist.all_gather_into_tensor(d_X, d_shard)
-        else:
-            d_X.copy_(h_X, non_blocking=True)
-        m = capi.preprocess(d_rp, my_nnz, 512, 32, 4)   # device-side row decomposition (reads 2 counts back)
-        C.zero_()                                        # the API's contract: C arrives zero-filled
+            dist.all_gather_into_tensor(d_X_full, bf["X"])
+        dense_x = d_X_full if world > 1 else bf["X"]
+        m = capi.preprocess(bf["rp"], my_nnz, 512, 32, 4)   # device-side row decomposition (reads 2 counts back)
+        bf["C"].zero_()                                       # the API's contract: C arrives zero-filled
 
         def launch(s1, s2):
-            capi.spmm_raw(torch.float32, m.m1, m.m2, n_vert, N_DENSE, d_val.data_ptr(), d_col.data_ptr(),
-                          d_rp.data_ptr(), m.block_r_ind.data_ptr(), m.residue_r_ind.data_ptr(), m.st_off.data_ptr(),
-                          d_X.data_ptr(), C.data_ptr(), ws.data_ptr(), ws_bytes, s1, s2)
+            capi.spmm_raw(torch.float32, m.m1, m.m2, n_vert, N_DENSE, bf["val"].data_ptr(), bf["col"].data_ptr(),
+                          bf["rp"].data_ptr(), m.block_r_ind.data_ptr(), m.residue_r_ind.data_ptr(),
+                          m.st_off.data_ptr(), dense_x.data_ptr(), bf["C"].data_ptr(), ws.data_ptr(), ws_bytes, s1, s2)
 
         fj.run(launch)
-        h_C.copy_(C, non_blocking=True)
+        bf["in_free"].record(fj.cur)
+        bf["out_ready"].record(fj.cur)
+        s_out.wait_event(bf["out_ready"])
+        with torch.cuda.stream(s_out):
+            h_C.copy_(bf["C"], non_blocking=True)
+            bf["out_free"].record(s_out)
 
-    e2e_step()
+    def e2e_run(steps):
+        copy_in(0)
+        for i in range(steps):
+            if i + 1 < steps:
+                copy_in(i + 1)
+            compute_and_copy_out(i)
+        fj.cur.wait_event(bufs[(steps - 1) % 2]["out_free"])   # the last result is on the host
+
+    e2e_run(1)
     barrier()
     a.record(fj.cur)
-    for _ in range(args.e2e_steps):
-        e2e_step()
+    e2e_run(args.e2e_steps)
     b.record(fj.cur)
     barrier()
     ms_e2e = max_over_ranks(a.elapsed_time(b) / args.e2e_steps)
     e2e = {"value": 2.0 * nnz * N_DENSE / ms_e2e / 1e6, "unit": "GFLOP/s", "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
-           "includes": ("H2D of the rank's CSR slice + dense operand from pinned memory, device preprocessing, "
-                        "C zero-fill, SpMM, D2H of the rank's C rows" if world == 1 else
-                        "per rank: H2D of its CSR slice + 1/N of the dense operand from pinned memory, NCCL "
-                        "all-gather of the operand, device preprocessing, C zero-fill, SpMM, D2H of its C rows; "
-                        "bytes are rank 0's")}
+           "includes": ("every step: H2D of the rank's CSR slice + dense operand from pinned memory, device "
+                        "preprocessing, C zero-fill, SpMM, D2H of the rank's C rows; steps are software-pipelined "
+                        "(step i+1's H2D overlaps step i's compute and D2H)" if world == 1 else
+                        "every step, per rank: H2D of its CSR slice + 1/N of the dense operand from pinned memory, "
+                        "NCCL all-gather of the operand, device preprocessing, C zero-fill, SpMM, D2H of its C rows; "
+                        "steps are software-pipelined; bytes are rank 0's")}
     checksum = float(h_C.double().sum())
 
     # ---- CPU baseline (rank 0, single-GPU run only) ----------------------------------------------
@@ -654,7 +688,7 @@ def main():
                         "single_thread_value": 2.0 * nnz_1 * N_DENSE / dt1 / 1e9,
                         "single_thread_sample": f"rows 0..{rows_1} (nnz {nnz_1}), one pass, {dt1:.2f} s",
                         "note": "the reference has no CPU SpMM; this is the oracle's CSR SpMM with OpenMP over rows"}
-        del h_rp, h_col, h_val, h_X, h_C, d_rp, d_col, d_val, d_X
+        del h_rp, h_col, h_val, h_X, h_C, bufs
         torch.cuda.empty_cache()
         configs = secondary_configs(peak_gbs, min(args.steps, 10), 3)
 
