@@ -299,7 +299,22 @@ def secondary_configs(peak_gbs, steps, warmup):
                 bmin = sddmm_bmin(A.nnz, A.m, width, m_nonempty, k_touched)
                 # the reference SDDMM skips a kernel on a null stream and has K = 32 / 128 only
                 ref_ok = have_ref and width in (32, 128) and meta.m1 > 0 and meta.m2 > 0 and (A.n - 1) * width < 2**29
+            # context column: the vendor library through torch (cuSPARSE SpMM / sampled_addmm)
+            lib_ms = None
+            try:
+                csr_t = torch.sparse_csr_tensor(A.row_ptr.long(), A.col.long(), A.val, size=(A.m, A.n))
+                if op == "spmm":
+                    lib_fn = lambda: torch.sparse.mm(csr_t, B)  # noqa: E731
+                else:
+                    rhs_t = rhs.t()
+                    lib_fn = lambda: torch.sparse.sampled_addmm(csr_t, lhs, rhs_t, beta=0.0)  # noqa: E731
+                lib_ms = time_loop(lib_fn, min(steps, 5), 2, fj.cur, flush)
+                del csr_t
+            except Exception as exc:  # library path unavailable for this shape: leave the column empty
+                entry["vendor_library_error"] = str(exc)[:120]
             ms = time_loop(lambda: fj.run(ours), steps, warmup, fj.cur, flush)
+            if lib_ms is not None:
+                entry.update({"vendor_library_ms": lib_ms, "speedup_vs_vendor_library": lib_ms / ms})
             entry.update({"ms": ms, "gflops": 2.0 * A.nnz * width / ms / 1e6, "bmin_bytes": bmin,
                           "algorithmic_gbs": bmin / ms / 1e6, "frac_of_measured_hbm": bmin / ms / 1e6 / peak_gbs})
             if ref_ok:

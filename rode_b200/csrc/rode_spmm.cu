@@ -392,8 +392,9 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
     constexpr int U = 8 < L ? 8 : L;
     constexpr int kAlign = 4;
     constexpr int kBlockK = 32;
-    const int item = (blockIdx.x * kRowsCtaThreads + threadIdx.x) / L;
-    if (item >= m2) return;
+    const long long item_ll = (static_cast<long long>(blockIdx.x) * kRowsCtaThreads + threadIdx.x) / L;
+    if (item_ll >= m2) return;
+    const int item = static_cast<int>(item_ll);
     const int lane = threadIdx.x & 31;
     const int l = lane % L;
     const unsigned gmask = group_mask<L>(lane);

@@ -172,3 +172,18 @@ def test_spmm_full_size_properties(oracle_cpu, family, n):
     resid = (C3 - (2 * C1 - C2)).abs().max().item()
     assert resid <= 1e-3 * max(1.0, C1.abs().max().item()), resid
     del C2, C3
+
+
+def test_spmm_matches_reference_kernel_fixtures(oracle_cpu, golden_dir):
+    """tests/golden/spmm_golden.npz: outputs of the reference's own SpMM kernels."""
+    import os
+
+    g = np.load(os.path.join(golden_dir, "spmm_golden.npz"))
+    for case in sorted({k.split("/")[0] for k in g.files}):
+        a = {k: g[f"{case}/{k}"] for k in ("row_ptr", "col", "val", "B", "C")}
+        A = W.CSR(len(a["row_ptr"]) - 1, a["B"].shape[0], torch.from_numpy(a["row_ptr"]), torch.from_numpy(a["col"]),
+                  torch.from_numpy(a["val"]))
+        d, meta = gpu_inputs(A)
+        C = capi.spmm(meta, d.row_ptr, d.col, d.val, torch.from_numpy(a["B"]).cuda())
+        scale = spmm_abs_scale(a["row_ptr"], a["col"], a["val"], a["B"])
+        assert_close_to_truth(C.cpu().numpy(), a["C"].astype(np.float64), 2 * scale, case)

@@ -113,3 +113,26 @@ def test_spmm_oracle_against_dense_numpy(oracle_cpu):
     assert np.allclose(oracle_cpu.spmm_f32(rp, col, val, B, threads=2), truth, rtol=1e-5, atol=1e-5)
     assert np.allclose(oracle_cpu.spmm_f64(rp, col, val, B), truth, rtol=1e-12, atol=1e-12)
     assert np.array_equal(oracle_cpu.spmm_f32(rp, col, val, B)[5], np.zeros(n, np.float32))
+
+
+def test_spmm_oracle_matches_reference_kernel_fixtures(oracle_cpu, golden_dir):
+    """spmm_golden.npz holds results of the reference's own GPU SpMM kernels (generated by
+    tests/golden/make_golden_gpu.py); the fp32 oracle and the fp64 ground truth agree with
+    them within the tolerance of the parity tests."""
+    import os
+
+    from tests.helpers import assert_close_to_truth, spmm_abs_scale
+
+    path = os.path.join(golden_dir, "spmm_golden.npz")
+    if not os.path.exists(path):
+        pytest.skip("spmm_golden.npz not generated yet (needs a GPU run of make_golden_gpu.py)")
+    g = np.load(path)
+    cases = sorted({k.split("/")[0] for k in g.files})
+    assert len(cases) >= 3
+    for case in cases:
+        a = {k: g[f"{case}/{k}"] for k in ("row_ptr", "col", "val", "B", "C")}
+        truth = oracle_cpu.spmm_f64acc(a["row_ptr"], a["col"], a["val"], a["B"])
+        scale = spmm_abs_scale(a["row_ptr"], a["col"], a["val"], a["B"])
+        assert_close_to_truth(a["C"], truth, scale, f"reference kernels, {case}")
+        assert_close_to_truth(oracle_cpu.spmm_f32(a["row_ptr"], a["col"], a["val"], a["B"]), a["C"].astype(np.float64),
+                              2 * scale, f"oracle vs reference kernels, {case}")
