@@ -4,10 +4,13 @@
 // :41-195) and their launcher (:492-529).  The work split follows the reference's metadata
 // (block segments, residue rows); how the work is done is new:
 //
-//  * A dense-row slice of the column tile is covered by L lanes, 16 bytes per lane (one
-//    LDG.128), so a gather of B[col, tile] is one coalesced request of 16*L bytes.
-//    L = 8, 16 or 32; a warp holds G = 32/L such lane groups.
-//  * Gathers are issued in batches of U = 8 independent LDG.128 per lane; the (column,
+//  * A dense-row slice of the column tile (8, 16 or 32 vectors of 16 bytes) is covered by a
+//    lane group of L lanes with VPL vectors per lane (LDG.128 each): 4 x 2 for 8 vectors,
+//    8 x 2 for 16, 32 x 1 for 32.  Two vectors per lane halve the shuffles and the address
+//    arithmetic per byte (measured: N = 32 power-law 0.68 -> 0.58 ms, N = 64 R-MAT-21
+//    0.99 -> 0.75 ms, N = 64 stencil 0.97 -> 0.75 ms; for 32 vectors no shape beat 32 x 1).
+//    A warp holds G = 32/L lane groups.
+//  * Gathers are issued in batches of 8 independent LDG.128 per lane; the (column,
 //    value) pairs of a chunk of 32 nonzeros are fetched two chunks ahead and handed to the
 //    lanes by shuffles.  Bytes in flight per SM = resident warps x 32 x U x 16 B, so the
 //    kernels are kept at 64 registers (32 one-warp CTAs per SM, ~131 KB in flight).  Two
@@ -45,40 +48,45 @@ namespace {
 #ifndef RODE_SPMM_CTA_WARPS
 #define RODE_SPMM_CTA_WARPS 1
 #endif
-#ifndef RODE_SPMM_U32
-#define RODE_SPMM_U32 8
-#endif
-#ifndef RODE_SPMM_U16
-#define RODE_SPMM_U16 8
-#endif
-#ifndef RODE_SPMM_U8
-#define RODE_SPMM_U8 8
-#endif
 // Small CTAs: a CTA's slot is held until its slowest warp is done, and segments differ in
 // length by more than 10x, so fewer warps per CTA keep more warps resident on average.
 constexpr int kCtaWarps = RODE_SPMM_CTA_WARPS;
 constexpr int kCtaThreads = 32 * kCtaWarps;
 
-// Dense rows per register batch = independent 16-byte loads a lane keeps in flight.
-template <int L>
-struct Batch {
-    static constexpr int kRows = (L == 32) ? RODE_SPMM_U32 : (L == 16) ? RODE_SPMM_U16 : RODE_SPMM_U8;
-};
+// Shape of a lane group per tile width (in 16-byte vectors: 8, 16 or 32 per dense-row slice):
+// L lanes x VPL vectors per lane, encoded as L * 100 + VPL.
+#ifndef RODE_SPMM_SHAPE_8
+#define RODE_SPMM_SHAPE_8 402
+#endif
+#ifndef RODE_SPMM_SHAPE_16
+#define RODE_SPMM_SHAPE_16 802
+#endif
+#ifndef RODE_SPMM_SHAPE_32
+#define RODE_SPMM_SHAPE_32 3201
+#endif
+// Residue rows of 32-vector tiles may use another shape than the block kernel (3201 selects
+// the batched spmm_rows kernel).
+#ifndef RODE_SPMM_ROWS_SHAPE_32
+#define RODE_SPMM_ROWS_SHAPE_32 3201
+#endif
+// 16-byte loads a lane keeps in flight per batch (dense rows per batch = this / VPL).
+constexpr int kLoadsInFlight = 8;
 
 // ---------------------------------------------------------------------------------------
-// One warp per block segment; grid.y walks the column tiles of width L * kLen.  U = dense
-// rows per batch (loads in flight per lane): 8 for grids that fill the GPU (64 registers keep
-// 32 warps per SM resident); the whole chunk (U = L) for small grids, where the time is the
+// One warp per block segment; grid.y walks the column tiles of L * VPL vectors.  U = dense
+// rows per batch: kLoadsInFlight / VPL for grids that fill the GPU (64 registers keep 32
+// warps per SM resident); the whole chunk for small grids, where the time is the
 // dependent-batch chain of the longest segment and registers are free.
-template <typename T, int L, int U>
-__global__ void __launch_bounds__(kCtaThreads, (U > Batch<L>::kRows) ? 1 : 32 / kCtaWarps)
+template <typename T, int L, int VPL, int U>
+__global__ void __launch_bounds__(kCtaThreads, (U * VPL > kLoadsInFlight) ? 1 : 32 / kCtaWarps)
 spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
            const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
            const int *__restrict__ st_off, const T *__restrict__ B, T *__restrict__ C, T *__restrict__ partial) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
     constexpr int G = 32 / L;             // lane groups, each takes every G-th nonzero
-    constexpr int NB = (L + U - 1) / U;   // batches per 32-nonzero chunk
+    constexpr int kSteps = 32 / G;        // nonzeros per group per 32-nonzero chunk
+    constexpr int NB = (kSteps + U - 1) / U;
     constexpr unsigned kFull = 0xffffffffu;
     const int seg = blockIdx.x * kCtaWarps + (threadIdx.x >> 5);
     if (seg >= m1) return;
@@ -94,7 +102,7 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     const bool whole_row = (off == row_begin) && (next >= row_end);
 
     const size_t row_vecs = static_cast<size_t>(n) / kLen;
-    const size_t col_vec = static_cast<size_t>(blockIdx.y) * L + l;
+    const size_t col_vec = static_cast<size_t>(blockIdx.y) * L * VPL + l;  // + v * L for vector v
     const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
 
     // (column, value) of this lane's nonzero in the current and in the next chunk
@@ -109,7 +117,9 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
         v_nxt = ld_stream(values + off + 32 + lane);
     }
 
-    V acc = vzero(static_cast<V *>(nullptr));
+    V acc[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) acc[v] = vzero(static_cast<V *>(nullptr));
     for (int base = off; base < end; base += 32) {
         const int cnt = min(32, end - base);
         int c_pre = 0;
@@ -121,18 +131,23 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
             if (b * U * G >= cnt) break;  // warp-uniform
-            V buf[U];
+            V buf[U][VPL];
             T vv[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int t = (b * U + u) * G + g;  // position inside the chunk
-                const int c = __shfl_sync(kFull, c_cur, t);
-                vv[u] = __shfl_sync(kFull, v_cur, t);
-                buf[u] = vzero(static_cast<V *>(nullptr));
-                if (t < cnt) buf[u] = ld_dense(b_lane + static_cast<size_t>(c) * row_vecs);
+                const int c = __shfl_sync(kFull, c_cur, t & 31);
+                vv[u] = __shfl_sync(kFull, v_cur, t & 31);
+#pragma unroll
+                for (int v = 0; v < VPL; ++v) {
+                    buf[u][v] = vzero(static_cast<V *>(nullptr));
+                    if (t < cnt) buf[u][v] = ld_dense(b_lane + static_cast<size_t>(c) * row_vecs + v * L);
+                }
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u) vfma(acc, vv[u], buf[u]);
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int v = 0; v < VPL; ++v) vfma(acc[v], vv[u], buf[u][v]);
         }
         c_cur = c_nxt;
         v_cur = v_nxt;
@@ -144,13 +159,18 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     // completion before it reads the workspace).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
-    for (int w = L; w < 32; w <<= 1) vadd(acc, vshfl_xor(kFull, acc, w));
+    for (int v = 0; v < VPL; ++v)
+#pragma unroll
+        for (int w = L; w < 32; w <<= 1) vadd(acc[v], vshfl_xor(kFull, acc[v], w));
 
     if (g == 0) {
-        if (whole_row)
-            st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec, acc);
-        else
-            reinterpret_cast<V *>(partial)[static_cast<size_t>(seg) * row_vecs + col_vec] = acc;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            if (whole_row)
+                st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec + v * L, acc[v]);
+            else
+                reinterpret_cast<V *>(partial)[static_cast<size_t>(seg) * row_vecs + col_vec + v * L] = acc[v];
+        }
     }
 }
 
@@ -245,7 +265,7 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
           const int *__restrict__ residue_r_ind, const T *__restrict__ B, T *__restrict__ C) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
-    constexpr int U = (Batch<L>::kRows < L) ? Batch<L>::kRows : L;  // rows per batch
+    constexpr int U = (kLoadsInFlight < L) ? kLoadsInFlight : L;  // rows per batch
     constexpr int NB = (L + U - 1) / U;  // batches per L-nonzero chunk
     constexpr int kAlign = 4;            // vec_len of the preprocessing
     constexpr int kBlockK = 32;          // k_block of the preprocessing
@@ -369,29 +389,25 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
 }
 
 // ---------------------------------------------------------------------------------------
-// Residue rows without a block part, one lane group per row (no batching of rows).  Used for
-// L = 8 and 16: there the lane groups of a warp would run different entry streams in
-// spmm_rows and diverge, which measured slower (stencil N = 64: 1.43 ms against 0.93 ms;
-// power-law N = 32: 331 us against 283 us) while for L = 32 the batched kernel wins
-// (R-MAT N = 128: 327 us against 770 us).
+// Residue rows without a block part, one lane group (L lanes x VPL vectors) per row.  Used
+// where a warp holds several groups: there the groups would run different entry streams in
+// spmm_rows and diverge, which measured slower (stencil N = 64: 1.43 ms against 0.93 ms),
+// while for 32-lane groups the batched kernel wins (R-MAT N = 128: 327 us against 770 us).
 #ifndef RODE_SPMM_ROWS_CTA
-#define RODE_SPMM_ROWS_CTA 64
-#endif
-#ifndef RODE_SPMM_ROWS_SIMPLE_MASK
-#define RODE_SPMM_ROWS_SIMPLE_MASK 3  // bit 0: L = 8, bit 1: L = 16, bit 2: L = 32
+#define RODE_SPMM_ROWS_CTA 32
 #endif
 constexpr int kRowsCtaThreads = RODE_SPMM_ROWS_CTA;
 
-template <typename T, int L>
+template <typename T, int L, int VPL>
 __global__ void __launch_bounds__(kRowsCtaThreads)
 spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
                  const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind,
                  const T *__restrict__ B, T *__restrict__ C) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
-    constexpr int U = 8 < L ? 8 : L;
-    constexpr int kAlign = 4;
-    constexpr int kBlockK = 32;
+    constexpr int U = (kLoadsInFlight / VPL < L) ? kLoadsInFlight / VPL : L;
+    constexpr int kAlign = 4;    // vec_len of the preprocessing
+    constexpr int kBlockK = 32;  // k_block of the preprocessing
     const long long item_ll = (static_cast<long long>(blockIdx.x) * kRowsCtaThreads + threadIdx.x) / L;
     if (item_ll >= m2) return;
     const int item = static_cast<int>(item_ll);
@@ -402,20 +418,23 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
     const int row = __ldg(residue_r_ind + item);
     const int begin = __ldg(row_offsets + row);
     const int end = __ldg(row_offsets + row + 1);
+    // aligned length >= k_block: a block part exists and its last segment took the tail
     if (end - begin + (begin % kAlign) >= kBlockK) return;
 
     const size_t row_vecs = static_cast<size_t>(n) / kLen;
-    const size_t col_vec = static_cast<size_t>(blockIdx.y) * L + l;
+    const size_t col_vec = static_cast<size_t>(blockIdx.y) * L * VPL + l;
     const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
 
-    V acc = vzero(static_cast<V *>(nullptr));
+    V acc[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) acc[v] = vzero(static_cast<V *>(nullptr));
     for (int base = begin; base < end; base += L) {
         const int e = base + l;
         int c = 0;
-        T v = T(0);
+        T val = T(0);
         if (e < end) {
             c = ld_stream(column_indices + e);
-            v = ld_stream(values + e);
+            val = ld_stream(values + e);
         }
         const int cnt = min(L, end - base);
 #pragma unroll
@@ -423,22 +442,28 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
             if (t0 >= cnt) break;
             int cc[U];
             T vv[U];
-            V bb[U];
+            V bb[U][VPL];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 cc[u] = __shfl_sync(gmask, c, t0 + u, L);
-                vv[u] = __shfl_sync(gmask, v, t0 + u, L);
+                vv[u] = __shfl_sync(gmask, val, t0 + u, L);
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                bb[u] = vzero(static_cast<V *>(nullptr));
-                if (t0 + u < cnt) bb[u] = ld_dense(b_lane + static_cast<size_t>(cc[u]) * row_vecs);
-            }
+            for (int u = 0; u < U; ++u)
 #pragma unroll
-            for (int u = 0; u < U; ++u) vfma(acc, vv[u], bb[u]);
+                for (int v = 0; v < VPL; ++v) {
+                    bb[u][v] = vzero(static_cast<V *>(nullptr));
+                    if (t0 + u < cnt) bb[u][v] = ld_dense(b_lane + static_cast<size_t>(cc[u]) * row_vecs + v * L);
+                }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int v = 0; v < VPL; ++v) vfma(acc[v], vv[u], bb[u][v]);
         }
     }
-    st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec, acc);
+#pragma unroll
+    for (int v = 0; v < VPL; ++v)
+        st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec + v * L, acc[v]);
 }
 
 int sm_count() {
@@ -453,22 +478,30 @@ int sm_count() {
     return cached[dev];
 }
 
-template <typename T, int L>
-int launch_width(int m1, int m2, int n, const T *values, const int *col, const int *row_offsets,
+template <typename T, int L, int VPL>
+int launch_rows(int m2, int n, const T *values, const int *col, const int *row_offsets, const int *residue_r_ind,
+                const T *B, T *C, cudaStream_t s2);
+
+template <typename T, int L, int VPL, int RL, int RVPL>
+int launch_shape(int m1, int m2, int n, const T *values, const int *col, const int *row_offsets,
                  const int *block_r_ind, const int *residue_r_ind, const int *st_off, const T *B, T *C,
                  T *partial, cudaStream_t s1, cudaStream_t s2) {
-    constexpr int kTileWidth = L * Vec16<T>::kLen;
+    static_assert(L * VPL == RL * RVPL, "block and residue kernels must cover the same tile");
+    constexpr int kTileWidth = L * VPL * Vec16<T>::kLen;
+    constexpr int U = kLoadsInFlight / VPL;                      // rows per batch, large grids
+    constexpr int kChunkSteps = L;                               // nonzeros per group per chunk
+    constexpr int USmall = (kChunkSteps * VPL <= 32) ? kChunkSteps : 32 / VPL;  // small grids
     const unsigned tiles = static_cast<unsigned>(n / kTileWidth);
     if (m1 > 0) {
         dim3 grid((m1 + kCtaWarps - 1) / kCtaWarps, tiles);
         // fewer warps than two full waves of 32 per SM: latency of the longest segment rules
         const bool small_grid = static_cast<long long>(m1) * tiles <= 2LL * 32 * sm_count();
-        if (small_grid && L > Batch<L>::kRows)
-            spmm_block<T, L, L><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets, block_r_ind,
-                                                              st_off, B, C, partial);
+        if (small_grid && USmall > U)
+            spmm_block<T, L, VPL, USmall><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets,
+                                                                        block_r_ind, st_off, B, C, partial);
         else
-            spmm_block<T, L, Batch<L>::kRows><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets,
-                                                                            block_r_ind, st_off, B, C, partial);
+            spmm_block<T, L, VPL, U><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets, block_r_ind,
+                                                                   st_off, B, C, partial);
         RODE_CHECK_LAUNCH("rode::spmm_block");
         // fix-up as a programmatic dependent of spmm_block: its launch latency and its
         // metadata prologue overlap the tail of the block grid
@@ -487,24 +520,32 @@ int launch_width(int m1, int m2, int n, const T *values, const int *col, const i
                                          C));
         RODE_CHECK_LAUNCH("rode::spmm_fixup");
     }
-    if (m2 > 0) {
-        constexpr int kBit = (L == 8) ? 1 : (L == 16) ? 2 : 4;
-        if (RODE_SPMM_ROWS_SIMPLE_MASK & kBit) {
+    if (m2 > 0) return launch_rows<T, RL, RVPL>(m2, n, values, col, row_offsets, residue_r_ind, B, C, s2);
+    return RODE_OK;
+}
+
+template <typename T, int L, int VPL>
+int launch_rows(int m2, int n, const T *values, const int *col, const int *row_offsets, const int *residue_r_ind,
+                const T *B, T *C, cudaStream_t s2) {
+    constexpr int kTileWidth = L * VPL * Vec16<T>::kLen;
+    const unsigned tiles = static_cast<unsigned>(n / kTileWidth);
+    {
+        if (L == 32 && VPL == 1) {
+            // 32 rows per warp when the list is long; fewer (shorter dependent chains, more
+            // warps) when the warps would not fill the GPU twice over
+            const long long slots = 2LL * 28 * sm_count() * (kCtaThreads / 32);
+            int per_group = static_cast<int>((m2 + slots - 1) / slots);
+            per_group = per_group < 4 ? 4 : (per_group > 32 ? 32 : per_group);
+            const long long groups = (static_cast<long long>(m2) + per_group - 1) / per_group;
+            constexpr int kGroupsPerCta = kCtaThreads / 32;
+            dim3 grid(static_cast<unsigned>((groups + kGroupsPerCta - 1) / kGroupsPerCta), tiles);
+            spmm_rows<T, 32><<<grid, kCtaThreads, 0, s2>>>(m2, per_group, n, values, col, row_offsets,
+                                                           residue_r_ind, B, C);
+        } else {
             constexpr int kRowsPerCta = kRowsCtaThreads / L;
             dim3 grid((m2 + kRowsPerCta - 1) / kRowsPerCta, tiles);
-            spmm_rows_simple<T, L><<<grid, kRowsCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets, residue_r_ind,
-                                                                      B, C);
-        } else {
-            // L rows per lane group when the list is long; fewer (shorter dependent chains,
-            // more warps) when the groups would not fill the GPU twice over
-            const long long slots = 2LL * 28 * sm_count() * (kCtaThreads / L);
-            int per_group = static_cast<int>((m2 + slots - 1) / slots);
-            per_group = per_group < 4 ? 4 : (per_group > L ? L : per_group);
-            const long long groups = (static_cast<long long>(m2) + per_group - 1) / per_group;
-            constexpr int kGroupsPerCta = kCtaThreads / L;
-            dim3 grid(static_cast<unsigned>((groups + kGroupsPerCta - 1) / kGroupsPerCta), tiles);
-            spmm_rows<T, L><<<grid, kCtaThreads, 0, s2>>>(m2, per_group, n, values, col, row_offsets,
-                                                          residue_r_ind, B, C);
+            spmm_rows_simple<T, L, VPL><<<grid, kRowsCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets,
+                                                                          residue_r_ind, B, C);
         }
         RODE_CHECK_LAUNCH("rode::spmm_rows");
     }
@@ -535,15 +576,15 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
         if (!aligned_to(workspace, 16)) return fail(RODE_ERR_WORKSPACE, "spmm: workspace must be 16-byte aligned");
     }
     T *partial = static_cast<T *>(workspace);
-    // Widest lane group whose tile divides n.
-    if (n % (32 * kLen) == 0)
-        return launch_width<T, 32>(m1, m2, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C,
-                                   partial, stream1, stream2);
-    if (n % (16 * kLen) == 0)
-        return launch_width<T, 16>(m1, m2, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C,
-                                   partial, stream1, stream2);
-    return launch_width<T, 8>(m1, m2, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C,
-                              partial, stream1, stream2);
+    // Widest tile (32, 16 or 8 vectors of 16 bytes) that divides the row.
+#define RODE_LAUNCH(shape, rows_shape)                                                                        \
+    launch_shape<T, (shape) / 100, (shape) % 100, (rows_shape) / 100, (rows_shape) % 100>(                     \
+        m1, m2, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, stream1, stream2)
+    const int vecs = n / kLen;
+    if (vecs % 32 == 0) return RODE_LAUNCH(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32);
+    if (vecs % 16 == 0) return RODE_LAUNCH(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16);
+    return RODE_LAUNCH(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8);
+#undef RODE_LAUNCH
 }
 
 }  // namespace
