@@ -35,36 +35,36 @@
 namespace rode {
 namespace {
 
-// Lanes per dense row for K = 32 / 64 / 128; with fewer lanes the rest of the row is covered
-// by several 16-byte loads per lane (VPL > 1).  Measured on B200: VPL = 2 costs 123 registers
-// and is slower than one load per lane (R-MAT-21 K = 64: 1.18 ms against 1.02 ms; power-law
-// K = 128: 2.64 ms against 2.39 ms), so the defaults keep VPL = 1.
-#ifndef RODE_SDDMM_L32
-#define RODE_SDDMM_L32 8
+// Shape of a lane group per K: L lanes x VPL 16-byte vectors per lane (K = 4 * L * VPL),
+// encoded as L * 100 + VPL.  A batch holds 8 / VPL nonzeros, so a lane always has 8 loads
+// in flight.
+#ifndef RODE_SDDMM_SHAPE_32
+#define RODE_SDDMM_SHAPE_32 801
 #endif
-#ifndef RODE_SDDMM_L64
-#define RODE_SDDMM_L64 16
+#ifndef RODE_SDDMM_SHAPE_64
+#define RODE_SDDMM_SHAPE_64 1601
 #endif
-#ifndef RODE_SDDMM_L128
-#define RODE_SDDMM_L128 32
+#ifndef RODE_SDDMM_SHAPE_128
+#define RODE_SDDMM_SHAPE_128 3201
 #endif
 #ifndef RODE_SDDMM_LONG_SEGMENTS_BY_WARP
 #define RODE_SDDMM_LONG_SEGMENTS_BY_WARP 1
 #endif
-constexpr int kBatch = 8;  // nonzeros per lane group per batch
+constexpr int kLoadsInFlight = 8;  // 16-byte loads per lane per batch
 constexpr unsigned kFull = 0xffffffffu;
 
 __device__ __forceinline__ float dot4(const float4 &a, const float4 &b, float acc) {
     return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, acc))));
 }
 
-// p[u] = this lane's share of the dot product of nonzero u of the batch (u = 0..7).
-// Returns the complete dot product of nonzero ((l / (L/8)) & 7) - the same value in the
-// L/8 lanes that share those bits.  All L lanes of the group named by gmask take part.
-template <int L>
-__device__ __forceinline__ float reduce_batch(float (&p)[kBatch], int l, unsigned gmask) {
+// p[u] = this lane's share of the dot product of nonzero u of the batch (u = 0..NB-1).
+// Returns the complete dot product of nonzero l / (L / NB) - the same value in the L / NB
+// lanes that share those bits.  All L lanes of the group named by gmask take part.
+template <int L, int NB>
+__device__ __forceinline__ float reduce_batch(float (&p)[NB], int l, unsigned gmask) {
+    static_assert(NB <= L, "a batch cannot hold more nonzeros than the group has lanes");
 #pragma unroll
-    for (int keep = kBatch / 2, w = L / 2; keep >= 1; keep >>= 1, w >>= 1) {
+    for (int keep = NB / 2, w = L / 2; keep >= 1; keep >>= 1, w >>= 1) {
         const bool upper = (l & w) != 0;
 #pragma unroll
         for (int i = 0; i < keep; ++i) {
@@ -75,7 +75,7 @@ __device__ __forceinline__ float reduce_batch(float (&p)[kBatch], int l, unsigne
     }
     float r = p[0];
 #pragma unroll
-    for (int w = L / 16; w >= 1; w >>= 1) r += __shfl_xor_sync(gmask, r, w, L);
+    for (int w = L / (2 * NB); w >= 1; w >>= 1) r += __shfl_xor_sync(gmask, r, w, L);
     return r;
 }
 
@@ -88,7 +88,8 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
             const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,
             float *__restrict__ out) {
     constexpr int G = 32 / L;
-    constexpr size_t kRowVecs = L * VPL;  // float4 per dense row (K / 4)
+    constexpr int kBatch = kLoadsInFlight / VPL;  // nonzeros per batch
+    constexpr size_t kRowVecs = L * VPL;          // float4 per dense row (K / 4)
     constexpr int kAlign = 4;             // vec_len of the preprocessing
     constexpr int kBlockK = 32;           // k_block of the preprocessing
     __shared__ int s_end[32];             // stream position where item j ends
@@ -225,8 +226,8 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
                     p[u] = d;
                     ++pos;
                 }
-                const float r = reduce_batch<L>(p, l, gmask);
-                // nonzero u of the batch sits in lanes u * (L/8) ..; lane b*8 + u of the group wants it
+                const float r = reduce_batch<L, kBatch>(p, l, gmask);
+                // nonzero u of the batch sits in lanes u * (L / kBatch) ..; lane b * kBatch + u wants it
                 const float got = (L == kBatch) ? r : __shfl_sync(gmask, r, (l & (kBatch - 1)) * (L / kBatch), L);
                 if ((l / kBatch) == b) mine = got;
             }
@@ -241,61 +242,35 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
     }
 }
 
-// Dot products of one chunk.  Lane t of the warp holds column `c` of nonzero t; `cnt`
-// nonzeros of the chunk are valid.  Group g handles nonzeros g*L .. g*L+L-1 with the lhs
-// slice `a`.  Returns, in lane t, the dot product of nonzero t.
-template <int L>
-__device__ __forceinline__ float chunk_dots(const float4 &a, int c, int cnt, const float4 *__restrict__ rhs_lane,
-                                            size_t row_vecs, int lane) {
-    const int l = lane % L;
-    const int gbase = lane - l;  // first lane (= first nonzero) of this group
-    const unsigned gmask = group_mask<L>(lane);
-    float mine = 0.f;
-#pragma unroll
-    for (int b = 0; b < L / kBatch; ++b) {
-        if (gbase + b * kBatch >= cnt) break;  // uniform inside the group
-        float4 bb[kBatch];
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
-            const int t = b * kBatch + u;  // nonzero inside the group's part of the chunk
-            const int cc = __shfl_sync(gmask, c, t, L);
-            bb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (gbase + t < cnt) bb[u] = ld_dense(rhs_lane + static_cast<size_t>(cc) * row_vecs);
-        }
-        float p[kBatch];
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u) p[u] = dot4(a, bb[u], 0.f);
-        const float r = reduce_batch<L>(p, l, gmask);
-        // nonzero u of the batch sits in lanes u * (L/8) ..; lane b*8 + u of the group wants it
-        const float got = __shfl_sync(gmask, r, (l & (kBatch - 1)) * (L / kBatch), L);
-        if ((l / kBatch) == b) mine = got;
-    }
-    return mine;
-}
-
 // ---------------------------------------------------------------------------------------
 // One warp per block segment (used where segments are long, K = 32 and 64: up to 543
 // nonzeros): coalesced chunk loads without any search, the G groups take consecutive
 // L-nonzero pieces of each 32-nonzero chunk, the lhs slice stays in registers.
-template <int L>
+template <int L, int VPL>
 __global__ void __launch_bounds__(32)
-sddmm_block(int m1, int k, const int *__restrict__ block_r_ind, const int *__restrict__ st_off,
+sddmm_block(int m1, const int *__restrict__ block_r_ind, const int *__restrict__ st_off,
             const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
             const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,
             float *__restrict__ out) {
+    constexpr int kBatch = kLoadsInFlight / VPL;
+    constexpr size_t kRowVecs = L * VPL;
     const int seg = blockIdx.x;
     if (seg >= m1) return;
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x;
     const int l = lane % L;
+    const int gbase = lane - l;  // first lane (= first nonzero of the chunk) of this group
+    const unsigned gmask = group_mask<L>(lane);
 
     const int row = __ldg(block_r_ind + seg);
     const int off = __ldg(st_off + seg);
     const int next = (seg + 1 < m1) ? __ldg(st_off + seg + 1) : INT_MAX;
     const int end = min(__ldg(row_offsets + row + 1), next);
 
-    const size_t row_vecs = static_cast<size_t>(k) / 4;
-    const float4 a = __ldg(reinterpret_cast<const float4 *>(lhs) + static_cast<size_t>(row) * row_vecs + l);
     const float4 *rhs_lane = reinterpret_cast<const float4 *>(rhs) + l;
+    float4 a[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v)
+        a[v] = __ldg(reinterpret_cast<const float4 *>(lhs) + static_cast<size_t>(row) * kRowVecs + v * L + l);
 
     int c_cur = 0, c_nxt = 0;
     float v_cur = 0.f, v_nxt = 0.f;
@@ -314,8 +289,36 @@ sddmm_block(int m1, int k, const int *__restrict__ block_r_ind, const int *__res
             c_pre = ld_stream(column_indices + base + 64 + lane);
             v_pre = ld_stream(values + base + 64 + lane);
         }
-        const float d = chunk_dots<L>(a, c_cur, min(32, end - base), rhs_lane, row_vecs, lane);
-        if (base + lane < end) st_stream(out + base + lane, v_cur * d);
+        const int cnt = min(32, end - base);
+        float mine = 0.f;
+#pragma unroll
+        for (int b = 0; b < L / kBatch; ++b) {
+            if (gbase + b * kBatch < cnt) {  // uniform inside the group
+                float4 bb[kBatch][VPL];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const int t = b * kBatch + u;  // nonzero inside the group's part of the chunk
+                    const int cc = __shfl_sync(gmask, c_cur, t, L);
+#pragma unroll
+                    for (int v = 0; v < VPL; ++v) {
+                        bb[u][v] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (gbase + t < cnt) bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc) * kRowVecs + v * L);
+                    }
+                }
+                float p[kBatch];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    float d = 0.f;
+#pragma unroll
+                    for (int v = 0; v < VPL; ++v) d = dot4(a[v], bb[u][v], d);
+                    p[u] = d;
+                }
+                const float r = reduce_batch<L, kBatch>(p, l, gmask);
+                const float got = (L == kBatch) ? r : __shfl_sync(gmask, r, (l & (kBatch - 1)) * (L / kBatch), L);
+                if ((l / kBatch) == b) mine = got;
+            }
+        }
+        if (base + lane < end) st_stream(out + base + lane, v_cur * mine);
         c_cur = c_nxt;
         v_cur = v_nxt;
         c_nxt = c_pre;
@@ -348,9 +351,8 @@ int launch_k(int m1, int m2, int seg_cap, const int *block_r_ind, const int *res
              const int *row_offsets, const int *col, const float *values, const float *lhs, const float *rhs,
              float *out, cudaStream_t s1, cudaStream_t s2) {
     if (m1 > 0) {
-        if (VPL == 1 && seg_cap < 32 && RODE_SDDMM_LONG_SEGMENTS_BY_WARP) {
-            sddmm_block<L><<<m1, 32, 0, s1>>>(m1, 4 * L, block_r_ind, st_off, row_offsets, col, values, lhs, rhs,
-                                              out);
+        if (seg_cap < 32 && RODE_SDDMM_LONG_SEGMENTS_BY_WARP) {
+            sddmm_block<L, VPL><<<m1, 32, 0, s1>>>(m1, block_r_ind, st_off, row_offsets, col, values, lhs, rhs, out);
             RODE_CHECK_LAUNCH("rode::sddmm_block");
         } else {
             const int per = items_per_warp(m1, seg_cap);
@@ -388,18 +390,18 @@ extern "C" int rode_sddmm_f32(int m1, int m2, int n, int k, const int *block_r_i
     if (!aligned_to(lhs, 16) || !aligned_to(rhs, 16))
         return fail(RODE_ERR_INVALID_ARGUMENT, "sddmm: lhs and rhs must be 16-byte aligned");
     switch (k) {
-        // (L, VPL) with K = 4 * L * VPL; segments per warp: few when segments are long (512)
+        // segments per warp in sddmm_items: few when segments are long (512), 32 when short
         case 32:
-            return launch_k<RODE_SDDMM_L32, 8 / RODE_SDDMM_L32>(m1, m2, 4, block_r_ind, residue_r_ind, st_off,
-                                                                 row_offsets, column_indices, values, lhs, rhs, out,
-                                                                 stream1, stream2);
+            return launch_k<RODE_SDDMM_SHAPE_32 / 100, RODE_SDDMM_SHAPE_32 % 100>(
+                m1, m2, 4, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values, lhs, rhs, out,
+                stream1, stream2);
         case 64:
-            return launch_k<RODE_SDDMM_L64, 16 / RODE_SDDMM_L64>(m1, m2, 4, block_r_ind, residue_r_ind, st_off,
-                                                                  row_offsets, column_indices, values, lhs, rhs, out,
-                                                                  stream1, stream2);
+            return launch_k<RODE_SDDMM_SHAPE_64 / 100, RODE_SDDMM_SHAPE_64 % 100>(
+                m1, m2, 4, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values, lhs, rhs, out,
+                stream1, stream2);
         default:
-            return launch_k<RODE_SDDMM_L128, 32 / RODE_SDDMM_L128>(m1, m2, 32, block_r_ind, residue_r_ind, st_off,
-                                                                    row_offsets, column_indices, values, lhs, rhs,
-                                                                    out, stream1, stream2);
+            return launch_k<RODE_SDDMM_SHAPE_128 / 100, RODE_SDDMM_SHAPE_128 % 100>(
+                m1, m2, 32, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values, lhs, rhs, out,
+                stream1, stream2);
     }
 }
