@@ -47,8 +47,9 @@ __device__ __forceinline__ void row_counts(int off, int next, int seg_len, int k
     }
 }
 
-// Inclusive scan of (x, y) over the CTA; returns the exclusive prefix of this thread and
-// the CTA totals.  smem: 2 * kWarps ints.
+// Inclusive scan of (x, y) over a CTA of kW warps; returns the exclusive prefix of this
+// thread and the CTA totals.  smem: 2 * kW ints.
+template <int kW = kWarps>
 __device__ __forceinline__ void block_exclusive_scan2(int x, int y, int *smem, int &ex, int &ey, int &tx,
                                                       int &ty) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -64,15 +65,15 @@ __device__ __forceinline__ void block_exclusive_scan2(int x, int y, int *smem, i
     }
     if (lane == 31) {
         smem[warp] = ix;
-        smem[kWarps + warp] = iy;
+        smem[kW + warp] = iy;
     }
     __syncthreads();
     int wx = 0, wy = 0;
     tx = 0;
     ty = 0;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        const int sx = smem[w], sy = smem[kWarps + w];
+    for (int w = 0; w < kW; ++w) {
+        const int sx = smem[w], sy = smem[kW + w];
         if (w < warp) {
             wx += sx;
             wy += sy;
@@ -110,19 +111,20 @@ count_tiles(int seg_len, int k_block, int vec_len, int M, const int *__restrict_
     if (threadIdx.x == 0) tile_totals[blockIdx.x] = make_int2(tx, ty);
 }
 
-// Single CTA.  Turns tile totals into exclusive tile offsets (in place) and publishes
-// n_blk, n_res and the end sentinel st_off[n_blk] = row_ptr[M].
-__global__ void __launch_bounds__(kThreads)
+// Single CTA of kScanThreads.  Turns tile totals into exclusive tile offsets (in place) and
+// publishes n_blk, n_res and the end sentinel st_off[n_blk] = row_ptr[M].
+constexpr int kScanThreads = 1024;
+__global__ void __launch_bounds__(kScanThreads)
 scan_tiles(int n_tiles, int M, const int *__restrict__ row_ptr, int2 *__restrict__ tile_totals,
            int *__restrict__ st_off, int *__restrict__ n_blk, int *__restrict__ n_res) {
-    __shared__ int smem[2 * kWarps];
+    __shared__ int smem[2 * (kScanThreads / 32)];
     int carry_b = 0, carry_r = 0;
-    for (int base = 0; base < n_tiles; base += kThreads) {
+    for (int base = 0; base < n_tiles; base += kScanThreads) {
         const int t = base + threadIdx.x;
         int2 v = make_int2(0, 0);
         if (t < n_tiles) v = tile_totals[t];
         int ex, ey, tx, ty;
-        block_exclusive_scan2(v.x, v.y, smem, ex, ey, tx, ty);
+        block_exclusive_scan2<kScanThreads / 32>(v.x, v.y, smem, ex, ey, tx, ty);
         if (t < n_tiles) tile_totals[t] = make_int2(carry_b + ex, carry_r + ey);
         carry_b += tx;
         carry_r += ty;
@@ -234,7 +236,7 @@ int launch_preprocess(int seg_len, int k_block, int vec_len, int M, const int *r
         count_tiles<<<n_tiles, kThreads, 0, stream>>>(seg_len, k_block, vec_len, M, row_ptr, tile_scratch);
         RODE_CHECK_LAUNCH("rode::count_tiles");
     }
-    scan_tiles<<<1, kThreads, 0, stream>>>(n_tiles, M, row_ptr, tile_scratch, st_off, n_blk, n_res);
+    scan_tiles<<<1, kScanThreads, 0, stream>>>(n_tiles, M, row_ptr, tile_scratch, st_off, n_blk, n_res);
     RODE_CHECK_LAUNCH("rode::scan_tiles");
     if (n_tiles > 0) {
         fill_tiles<<<n_tiles, kThreads, 0, stream>>>(seg_len, k_block, vec_len, M, row_ptr, tile_scratch,

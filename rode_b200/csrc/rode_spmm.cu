@@ -567,6 +567,8 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
     if (m2 > 0 && !residue_r_ind) return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: null residue metadata");
     if (!aligned_to(B, 16) || !aligned_to(C, 16))
         return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: B and C must be 16-byte aligned");
+    if (n / (8 * kLen) > 65535)
+        return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: n = %d exceeds the supported width (%d)", n, 65535 * 8 * kLen);
     size_t need = 0;
     rode_spmm_workspace_bytes(m1, n, static_cast<int>(sizeof(T)), &need);
     if (need > 0) {

@@ -1,0 +1,42 @@
+"""bench.py's command line on CPU: the reference arm prints exactly one JSON line with the
+agreed keys (bounded sample, oracle port on the host threads), and the product arm refuses to
+run without a GPU instead of falling back."""
+import json
+import os
+import subprocess
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(*args, env=None):
+    e = dict(os.environ)
+    e.update(env or {})
+    return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True,
+                          env=e, timeout=600)
+
+
+def test_reference_arm_prints_one_json_line(oracle_cpu):
+    res = _run("--impl", "reference", "--scale", "14", "--steps", "2", "--warmup", "1")
+    assert res.returncode == 0, res.stderr
+    lines = [l for l in res.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["unit"] == "GFLOP/s" and d["value"] > 0 and d["higher_is_better"] is True
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
+    assert d["e2e"] == {"value": d["value"], "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert d["config"]["workload"].endswith("spmm_n128") and d["steps"] == 2
+
+
+def test_reference_arm_other_ranks_exit_silently():
+    res = _run("--impl", "reference", "--gpus", "2", "--scale", "12", "--steps", "1", env={"RANK": "1", "WORLD_SIZE": "2"})
+    assert res.returncode == 0 and res.stdout.strip() == ""
+
+
+def test_product_arm_needs_a_gpu():
+    if torch.cuda.is_available():
+        return
+    res = _run("--steps", "1")
+    assert res.returncode != 0 and "no CPU path" in (res.stderr + res.stdout)
