@@ -69,6 +69,12 @@ constexpr int kCtaThreads = 32 * kCtaWarps;
 #ifndef RODE_SPMM_ROWS_SHAPE_32
 #define RODE_SPMM_ROWS_SHAPE_32 3201
 #endif
+// Widest column tile (in 16-byte vectors) a launch covers; narrower tiles walk the columns
+// in several passes over the sparse matrix (grid.y), which shrinks the dense working set of
+// each pass.
+#ifndef RODE_SPMM_MAX_TILE_VECS
+#define RODE_SPMM_MAX_TILE_VECS 32
+#endif
 // 16-byte loads a lane keeps in flight per batch (dense rows per batch = this / VPL).
 constexpr int kLoadsInFlight = 8;
 
@@ -583,7 +589,7 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
     launch_shape<T, (shape) / 100, (shape) % 100, (rows_shape) / 100, (rows_shape) % 100>(                     \
         m1, m2, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, stream1, stream2)
     const int vecs = n / kLen;
-    if (vecs % 32 == 0) return RODE_LAUNCH(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32);
+    if (vecs % 32 == 0 && RODE_SPMM_MAX_TILE_VECS >= 32) return RODE_LAUNCH(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32);
     if (vecs % 16 == 0) return RODE_LAUNCH(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16);
     return RODE_LAUNCH(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8);
 #undef RODE_LAUNCH
