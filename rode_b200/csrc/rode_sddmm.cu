@@ -247,7 +247,7 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
 // nonzeros): coalesced chunk loads without any search, the G groups take consecutive
 // L-nonzero pieces of each 32-nonzero chunk, the lhs slice stays in registers.
 template <int L, int VPL>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(32, 32)  // 64 registers: 32 one-warp CTAs per SM
 sddmm_block(int m1, const int *__restrict__ block_r_ind, const int *__restrict__ st_off,
             const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
             const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,

@@ -265,7 +265,7 @@ spmm_fixup(int m1, int n, const int *__restrict__ row_offsets, const int *__rest
 // Residue rows without a block part.  One lane group per L consecutive entries of
 // residue_r_ind; grid.y walks the column tiles.
 template <typename T, int L>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(kCtaThreads, (sizeof(T) == 4 ? 32 : 16) / kCtaWarps)  // fp32: 64 registers
 spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
           const int *__restrict__ column_indices, const int *__restrict__ row_offsets,
           const int *__restrict__ residue_r_ind, const T *__restrict__ B, T *__restrict__ C) {
