@@ -54,7 +54,7 @@ def parse_args():
     p.add_argument("--scale", type=int, default=23, help="R-MAT scale of the headline workload")
     p.add_argument("--no-extra", action="store_true", help="skip the secondary configs and the CPU baseline")
     p.add_argument("--e2e-steps", type=int, default=6)
-    p.add_argument("--row-weight", type=float, default=1.0,
+    p.add_argument("--row-weight", type=float, default=2.0,
                    help="multi-GPU partition: cost of a row = its nnz + this (0 = plain nnz-balanced)")
     p.add_argument("--only", choices=["spmm", "sddmm"], default=None,
                    help="small single-op run (one family, one width) for profiling and A/B timing")
