@@ -42,9 +42,11 @@ def _guards_intact(buf, n):
 def test_spmm_all_lengths_and_alignments(oracle_cpu, align):
     A = _sweep_matrix(align)
     d = A.to("cuda")
-    meta = capi.preprocess(d.row_ptr, d.nnz, 512, 32, 4)
     rp, col, val = A.row_ptr.numpy(), A.col.numpy(), A.val.numpy()
-    for n in (32, 64, 128, 96):
+    # segment length 512 is what the reference's SpMM uses; 32 (its SDDMM K = 128 setting) cuts
+    # rows into many more segments and exercises the workspace / fix-up path much harder
+    for seg, n in ((512, 32), (512, 64), (512, 128), (512, 96), (32, 32), (32, 128), (64, 64)):
+        meta = capi.preprocess(d.row_ptr, d.nnz, seg, 32, 4)
         B = W.dense(A.n, n, seed=n)
         buf, C = _guarded((A.m, n))
         C.zero_()
@@ -53,7 +55,7 @@ def test_spmm_all_lengths_and_alignments(oracle_cpu, align):
         capi.spmm(meta, d.row_ptr, d.col, d.val, B.cuda(), C=C, workspace=ws)
         torch.cuda.synchronize()
         truth = oracle_cpu.spmm_f64acc(rp, col, val, B.numpy())
-        assert_close_to_truth(C.cpu().numpy(), truth, spmm_abs_scale(rp, col, val, B.numpy()), f"align={align} n={n}")
+        assert_close_to_truth(C.cpu().numpy(), truth, spmm_abs_scale(rp, col, val, B.numpy()), f"align={align} seg={seg} n={n}")
         assert _guards_intact(buf, A.m * n) and _guards_intact(wbuf, max(ws_bytes // 4, 1))
 
 
