@@ -174,6 +174,40 @@ def time_loop(fn, steps, warmup, stream, flush=None):
     return statistics.median(times)
 
 
+def time_preprocess(row_ptr, nnz, seg, iters, peak_gbs, with_host=True):
+    """Device time of the three preprocessing kernels (raw entry point, buffers allocated
+    once), the host twin's single-thread time, and the HBM roofline of the device version:
+    algorithmic bytes = row pointer read once + outputs written once."""
+    from rode_b200 import capi
+
+    dev = row_ptr.device
+    M = row_ptr.numel() - 1
+    cap = capi.preprocess_capacity(seg, 4, M, nnz)
+    blk = torch.empty(max(cap, 1), dtype=torch.int32, device=dev)
+    st = torch.empty(cap + 1, dtype=torch.int32, device=dev)
+    res = torch.empty(max(M, 1), dtype=torch.int32, device=dev)
+    cnt = torch.zeros(2, dtype=torch.int32, device=dev)
+    ws_bytes = capi.preprocess_workspace_bytes(M)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def run():
+        capi.preprocess_raw(seg, 32, 4, M, row_ptr.data_ptr(), blk.data_ptr(), st.data_ptr(), res.data_ptr(),
+                            cnt.data_ptr(), cnt.data_ptr() + 4, ws.data_ptr(), ws_bytes, stream)
+
+    ms = time_loop(run, iters, 3, stream)
+    m1, m2 = cnt.cpu().tolist()
+    algo = 4 * (M + 1) + 8 * m1 + 4 + 4 * m2 + 8
+    out = {"seg_len": seg, "rows": M, "m1": m1, "m2": m2, "gpu_ms": ms, "algorithmic_bytes": algo,
+           "algorithmic_gbs": algo / ms / 1e6, "frac_of_measured_hbm": algo / ms / 1e6 / peak_gbs}
+    if with_host:
+        rp_host = row_ptr.cpu()
+        t0 = time.perf_counter()
+        capi.preprocess_cpu(rp_host, seg, 32, 4)
+        out["host_single_thread_ms"] = (time.perf_counter() - t0) * 1e3
+    return out
+
+
 class ForkJoin:
     """Runs the two-stream entry points so that one timing stream sees all of the work:
     block work on the current stream, residue work on a side stream forked from and joined
@@ -257,6 +291,8 @@ def secondary_configs(peak_gbs, steps, warmup):
             seg = 32 if (op == "sddmm" and width == 128) else 512
             meta = capi.preprocess(A.row_ptr, A.nnz, seg, 32, 4)
             entry = {"nnz": A.nnz, "m1": meta.m1, "m2": meta.m2}
+            pre = time_preprocess(A.row_ptr, A.nnz, seg, 10, peak_gbs, with_host=False)
+            entry["preprocess_gpu_ms"] = pre["gpu_ms"]
             if op == "spmm":
                 B = W.dense(A.n, width, device=dev, seed=3)
                 C = torch.zeros((A.m, width), device=dev)
@@ -512,6 +548,7 @@ def main():
         torch.cuda.empty_cache()
     my_nnz, my_rows = mine.nnz, mine.m
     meta = capi.preprocess(mine.row_ptr, my_nnz, 512, 32, 4)
+    preprocess_info = time_preprocess(mine.row_ptr, my_nnz, 512, 20, peak_gbs, with_host=(world == 1))
     C = torch.zeros((my_rows, N_DENSE), dtype=torch.float32, device=dev)
     ws_bytes = capi.spmm_workspace_bytes(meta.m1, N_DENSE, 4)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
@@ -719,7 +756,8 @@ def main():
                        "l2": "inputs larger than L2 (dense operand 4.3 GB, CSR 1 GB); no flush between steps",
                        "m1_rank0": meta.m1, "m2_rank0": meta.m2},
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps, "nnz_per_s": nnz / ms_step * 1e3,
-            "roofline": roofline, "e2e": e2e, "sddmm": sddmm, "cpu_baseline": cpu_baseline,
+            "roofline": roofline, "e2e": e2e, "sddmm": sddmm, "preprocess": preprocess_info,
+            "cpu_baseline": cpu_baseline,
             "broadcast_ms": broadcast_ms, "setup_s": setup_s, "checksum": checksum,
         }
         if configs is not None:
