@@ -280,7 +280,7 @@ def secondary_configs(peak_gbs, steps, warmup):
         ("cfg2_zipf65536", lambda: W.zipf_rows(device=dev), [("spmm", 128)]),
         ("cfg3_stencil128", lambda: W.stencil27(128, device=dev), [("spmm", 64), ("sddmm", 64)]),
         ("cfg4_pareto1m", lambda: W.pareto_rows(device=dev), [("spmm", 32), ("spmm", 128), ("sddmm", 32),
-                                                              ("sddmm", 128)]),
+                                                              ("sddmm", 128), ("spmm_f64", 32), ("spmm_f64", 128)]),
     ]
     for name, make, ops in specs:
         A = make()
@@ -293,28 +293,32 @@ def secondary_configs(peak_gbs, steps, warmup):
             entry = {"nnz": A.nnz, "m1": meta.m1, "m2": meta.m2}
             pre = time_preprocess(A.row_ptr, A.nnz, seg, 10, peak_gbs, with_host=False)
             entry["preprocess_gpu_ms"] = pre["gpu_ms"]
-            if op == "spmm":
-                B = W.dense(A.n, width, device=dev, seed=3)
-                C = torch.zeros((A.m, width), device=dev)
-                need = capi.spmm_workspace_bytes(meta.m1, width, 4)
+            if op in ("spmm", "spmm_f64"):
+                dt = torch.float64 if op == "spmm_f64" else torch.float32
+                esz = 8 if op == "spmm_f64" else 4
+                B = W.dense(A.n, width, device=dev, seed=3, dtype=dt)
+                vals = A.val.to(dt)
+                C = torch.zeros((A.m, width), device=dev, dtype=dt)
+                need = capi.spmm_workspace_bytes(meta.m1, width, esz)
                 ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
 
                 def ours(s1, s2):
-                    capi.spmm_raw(torch.float32, meta.m1, meta.m2, A.n, width, A.val.data_ptr(), A.col.data_ptr(),
+                    capi.spmm_raw(dt, meta.m1, meta.m2, A.n, width, vals.data_ptr(), A.col.data_ptr(),
                                   A.row_ptr.data_ptr(), meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(),
                                   meta.st_off.data_ptr(), B.data_ptr(), C.data_ptr(), ws.data_ptr(), need, s1, s2)
 
                 def theirs(s1, s2):
-                    ref.spmm_gpu(32 if width == 32 else 128, False, meta.m1, meta.m2, A.n, width, A.val.data_ptr(),
-                                 A.col.data_ptr(), A.row_ptr.data_ptr(), meta.block_r_ind.data_ptr(),
+                    ref.spmm_gpu(32 if width == 32 else 128, op == "spmm_f64", meta.m1, meta.m2, A.n, width,
+                                 vals.data_ptr(), A.col.data_ptr(), A.row_ptr.data_ptr(), meta.block_r_ind.data_ptr(),
                                  meta.residue_r_ind.data_ptr(), meta.st_off.data_ptr(), B.data_ptr(), C.data_ptr(),
                                  s1.cuda_stream, s2.cuda_stream)
 
-                bmin = spmm_bmin(A.nnz, A.m, width, k_touched)
+                bmin = (spmm_bmin(A.nnz, A.m, width, k_touched) if esz == 4 else
+                        12 * A.nnz + 4 * (A.m + 1) + 8 * width * k_touched + 8 * width * A.m)
                 # the reference's kernels: both grids non-empty, width 32 or a multiple of 64,
-                # and byte offsets col * n * 4 below 2^31
+                # and byte offsets col * n * sizeof(T) below 2^31
                 ref_ok = (have_ref and meta.m1 > 0 and meta.m2 > 0 and width in (32, 128)
-                          and (A.n - 1) * width * 4 < 2**31)
+                          and (A.n - 1) * width * esz < 2**31)
             else:
                 lhs = W.dense(A.m, width, device=dev, seed=5)
                 rhs = W.dense(A.n, width, device=dev, seed=6)
@@ -339,6 +343,8 @@ def secondary_configs(peak_gbs, steps, warmup):
             lib_ms = None
             try:
                 csr_t = torch.sparse_csr_tensor(A.row_ptr.long(), A.col.long(), A.val, size=(A.m, A.n))
+                if op == "spmm_f64":
+                    raise RuntimeError("fp64 comparison with the vendor library not timed")
                 if op == "spmm":
                     lib_fn = lambda: torch.sparse.mm(csr_t, B)  # noqa: E731
                 else:
@@ -369,7 +375,7 @@ def secondary_configs(peak_gbs, steps, warmup):
 
                 rms = time_loop(run_theirs, steps, warmup, fj.cur, flush)
                 entry.update({"reference_kernels_ms": rms, "speedup_vs_reference_kernels": rms / ms})
-            out[f"{name}_{op}{width}"] = entry
+            out[f"{name}_{op}{'_' if op.endswith('64') else ''}{width}"] = entry
             torch.cuda.synchronize()
         del A
         torch.cuda.empty_cache()
