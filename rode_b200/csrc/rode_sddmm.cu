@@ -207,6 +207,16 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
                     }
                 }
                 float p[kBatch];
+                if (cur_end - pos >= kBatch) {  // the whole batch lies inside the current item
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) {
+                        float d = 0.f;
+#pragma unroll
+                        for (int v = 0; v < VPL; ++v) d = dot4(a_cur[v], bb[u][v], d);
+                        p[u] = d;
+                    }
+                    pos += kBatch;
+                } else {
 #pragma unroll
                 for (int u = 0; u < kBatch; ++u) {
                     if (pos == cur_end && nxt >= 0) {  // the group enters its next item
@@ -225,6 +235,7 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
                     for (int v = 0; v < VPL; ++v) d = dot4(a_cur[v], bb[u][v], d);
                     p[u] = d;
                     ++pos;
+                }
                 }
                 const float r = reduce_batch<L, kBatch>(p, l, gmask);
                 // nonzero u of the batch sits in lanes u * (L / kBatch) ..; lane b * kBatch + u wants it
