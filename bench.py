@@ -612,6 +612,11 @@ def main():
         "frac": (block_bytes_all / world / ms_block / 1e6 / peak_gbs) if ms_block else None,
         "traffic": None, "algorithmic_bytes_per_launch": block_bytes_all / world, "ms_per_launch": ms_block,
         "residue_kernel_ms": ms_residue,
+        # upper bracket of the traffic model: every gather counted (no reuse of dense rows at all)
+        "no_reuse": {"bytes_per_launch": (8 * nnz_block + 4 * N_DENSE * nnz_block + 4 * N_DENSE * rows_block),
+                     "achieved": ((8 * nnz_block + 4 * N_DENSE * nnz_block + 4 * N_DENSE * rows_block) / ms_block / 1e6
+                                  if ms_block else None),
+                     "note": "rank 0's launch; bytes requested from L1/L2/HBM, of which `traffic` reach DRAM"},
         "step": {"algorithmic_bytes": step_bytes_all, "achieved": step_bytes_all / ms_step / 1e6,
                  "frac": step_bytes_all / ms_step / 1e6 / (peak_gbs * world)},
     }
