@@ -64,3 +64,21 @@ def test_partition_is_nnz_balanced_and_covers_all_rows():
     tiny = W.CSR(3, 4, torch.tensor([0, 0, 5, 5], dtype=torch.int32), torch.arange(5, dtype=torch.int32) % 4,
                  torch.ones(5))
     assert W.partition_rows(tiny.row_ptr, 4)[-1] == 3
+
+
+def test_row_weighted_partition_trades_nnz_for_rows():
+    A = W.rmat(scale=14, edge_factor=16)
+    rp = A.row_ptr.numpy().astype(np.int64)
+    plain = W.partition_rows(A.row_ptr, 8, 0.0)
+    weighted = W.partition_rows(A.row_ptr, 8, 2.0)
+    assert plain[0] == weighted[0] == 0 and plain[-1] == weighted[-1] == A.m and weighted == sorted(weighted)
+
+    def cost(b, w):
+        return [(rp[b[i + 1]] - rp[b[i]]) + w * (b[i + 1] - b[i]) for i in range(8)]
+
+    # the weighted cut equalises nnz + 2 * rows; the plain cut equalises nnz and leaves the last
+    # ranks with far more rows (R-MAT rows thin out towards high indices)
+    cw = cost(weighted, 2.0)
+    assert max(cw) / (sum(cw) / 8) < 1.05
+    assert max(cost(plain, 2.0)) > max(cw)
+    assert (plain[-1] - plain[-2]) > (weighted[-1] - weighted[-2])
