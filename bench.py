@@ -359,6 +359,21 @@ def secondary_configs(peak_gbs, steps, warmup):
                 entry.update({"vendor_library_ms": lib_ms, "speedup_vs_vendor_library": lib_ms / ms})
             entry.update({"ms": ms, "gflops": 2.0 * A.nnz * width / ms / 1e6, "bmin_bytes": bmin,
                           "algorithmic_gbs": bmin / ms / 1e6, "frac_of_measured_hbm": bmin / ms / 1e6 / peak_gbs})
+            if ms < 0.2:
+                # launch-bound sizes: the same three launches captured once in a CUDA graph and replayed
+                try:
+                    cap_stream, cap_side = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+                    graph = torch.cuda.CUDAGraph()
+                    torch.cuda.synchronize()
+                    with torch.cuda.graph(graph, stream=cap_stream):
+                        cap_side.wait_stream(cap_stream)
+                        ours(cap_stream, cap_side)
+                        cap_stream.wait_stream(cap_side)
+                    entry["graph_replay_ms"] = time_loop(graph.replay, steps, warmup, fj.cur, flush)
+                    del graph
+                except Exception as exc:
+                    entry["graph_replay_error"] = str(exc)[:160]
+                    torch.cuda.synchronize()
             if ref_ok:
                 side1 = torch.cuda.Stream(dev)  # the reference needs two real (non-null) streams
 

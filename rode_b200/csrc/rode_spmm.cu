@@ -30,11 +30,12 @@
 //    dependent chain row index -> row pointer -> column -> dense row is paid once per 32
 //    rows, not per row.  The nonzeros of the 32 rows form one entry stream that runs through
 //    the same batched gather; a row is stored when the stream passes its end.
-//    spmm_rows_simple (L = 8, 16): one lane group per residue row.
+//    spmm_rows_simple (L < 32): one lane group per residue row; spmm_rows_wide: one warp per
+//    row, for lists too short to fill the GPU.
 //    Empty rows in the list are stored as zeros, as the reference does
 //    (RoDeSpmm.cu:185-194); rows with a block part are skipped (spmm_block finished them).
-//  * CTAs are one warp (block, rows) or two (rows_simple): a CTA's slot is held until its
-//    slowest warp finishes, and segment lengths differ by more than 10x.
+//  * CTAs are one warp (four in spmm_rows_wide, whose rows are all shorter than 32): a CTA's
+//    slot is held until its slowest warp finishes, and segment lengths differ by more than 10x.
 //
 // Per nonzero the kernels move 8 B of CSR data and 16*L bytes of the dense operand (from
 // L1/L2/HBM depending on reuse); per row 4*n bytes of C.  Dense-row offsets are 64-bit.
@@ -52,6 +53,10 @@ namespace {
 // length by more than 10x, so fewer warps per CTA keep more warps resident on average.
 constexpr int kCtaWarps = RODE_SPMM_CTA_WARPS;
 constexpr int kCtaThreads = 32 * kCtaWarps;
+#ifndef RODE_SPMM_WIDE_ROWS_CTA_WARPS
+#define RODE_SPMM_WIDE_ROWS_CTA_WARPS 4
+#endif
+constexpr int kSmallGridWarps = RODE_SPMM_WIDE_ROWS_CTA_WARPS;  // rows (warps) per CTA of spmm_rows_wide
 
 // Shape of a lane group per tile width (in 16-byte vectors: 8, 16 or 32 per dense-row slice):
 // L lanes x VPL vectors per lane, encoded as L * 100 + VPL.
@@ -83,8 +88,8 @@ constexpr int kLoadsInFlight = 8;
 // rows per batch: kLoadsInFlight / VPL for grids that fill the GPU (64 registers keep 32
 // warps per SM resident); the whole chunk for small grids, where the time is the
 // dependent-batch chain of the longest segment and registers are free.
-template <typename T, int L, int VPL, int U>
-__global__ void __launch_bounds__(kCtaThreads, (U * VPL > kLoadsInFlight) ? 1 : 32 / kCtaWarps)
+template <typename T, int L, int VPL, int U, int W>
+__global__ void __launch_bounds__(32 * W, (U * VPL > kLoadsInFlight) ? 1 : 32 / W)
 spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
            const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
            const int *__restrict__ st_off, const T *__restrict__ B, T *__restrict__ C, T *__restrict__ partial) {
@@ -94,7 +99,12 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     constexpr int kSteps = 32 / G;        // nonzeros per group per 32-nonzero chunk
     constexpr int NB = (kSteps + U - 1) / U;
     constexpr unsigned kFull = 0xffffffffu;
-    const int seg = blockIdx.x * kCtaWarps + (threadIdx.x >> 5);
+    // Programmatic dependent launch: as soon as every CTA of this grid has started, the fix-up
+    // grid may be scheduled into free slots.  Its warps look for rows that were cut into
+    // several segments; those that find none exit at once, the others wait for this grid to
+    // complete before they read the workspace.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int seg = blockIdx.x * W + (threadIdx.x >> 5);
     if (seg >= m1) return;
     const int lane = threadIdx.x & 31;
     const int g = lane / L, l = lane % L;
@@ -160,10 +170,6 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
         c_nxt = c_pre;
         v_nxt = v_pre;
     }
-    // Programmatic dependent launch: once every warp of this grid is past its gathers, the
-    // fix-up grid may be scheduled and run its prologue (it still waits for this grid's
-    // completion before it reads the workspace).
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
 #pragma unroll
@@ -215,6 +221,7 @@ spmm_fixup(int m1, int n, const int *__restrict__ row_offsets, const int *__rest
         }
     }
     unsigned todo = __ballot_sync(kFull, head);
+    if (todo == 0) return;  // no split row among these 32 segments: nothing to wait for
     // Everything above read only the caller's metadata; the workspace is written by the
     // preceding spmm_block grid: wait for it (no-op when launched without the attribute).
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -403,9 +410,13 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
 #define RODE_SPMM_ROWS_CTA 32
 #endif
 constexpr int kRowsCtaThreads = RODE_SPMM_ROWS_CTA;
+// spmm_rows_wide (a warp per row) serves lists of at most this many full waves of warps
+#ifndef RODE_SPMM_WIDE_ROWS_WAVES
+#define RODE_SPMM_WIDE_ROWS_WAVES 2
+#endif
 
 template <typename T, int L, int VPL>
-__global__ void __launch_bounds__(kRowsCtaThreads)
+__global__ void __launch_bounds__(kRowsCtaThreads, 1024 / kRowsCtaThreads)  // 64 registers: 32 warps per SM
 spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
                  const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind,
                  const T *__restrict__ B, T *__restrict__ C) {
@@ -434,13 +445,23 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
     V acc[VPL];
 #pragma unroll
     for (int v = 0; v < VPL; ++v) acc[v] = vzero(static_cast<V *>(nullptr));
+    // Lane l keeps nonzero l of a chunk of L; the pair is fetched one chunk ahead, so that the
+    // fetch overlaps the gathers of the current chunk.
+    int c_nxt = 0;
+    T v_nxt = T(0);
+    if (begin + l < end) {
+        c_nxt = ld_stream(column_indices + begin + l);
+        v_nxt = ld_stream(values + begin + l);
+    }
     for (int base = begin; base < end; base += L) {
-        const int e = base + l;
-        int c = 0;
-        T val = T(0);
+        const int c = c_nxt;
+        const T val = v_nxt;
+        const int e = base + L + l;
+        c_nxt = 0;
+        v_nxt = T(0);
         if (e < end) {
-            c = ld_stream(column_indices + e);
-            val = ld_stream(values + e);
+            c_nxt = ld_stream(column_indices + e);
+            v_nxt = ld_stream(values + e);
         }
         const int cnt = min(L, end - base);
 #pragma unroll
@@ -472,6 +493,76 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
         st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec + v * L, acc[v]);
 }
 
+// ---------------------------------------------------------------------------------------
+// The same rows, one WARP per row: for residue lists too short to fill the GPU, where the
+// time of the launch is the dependent chain of one row, not throughput.  The 32 lanes fetch
+// the row's (fewer than 32) pairs in one coalesced load; the 32 / L lane groups then take
+// every (32 / L)-th nonzero each, so that all gathers of the row are in flight at once (L
+// per group), and a butterfly over the groups adds the partial rows.  Two dependent memory
+// round trips after the row's bounds are known, against up to 32 / L in spmm_rows_simple.
+template <typename T, int L, int VPL>
+__global__ void __launch_bounds__(32 * kSmallGridWarps, 1)
+spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
+               const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind,
+               const T *__restrict__ B, T *__restrict__ C) {
+    using V = typename Vec16<T>::type;
+    constexpr int kLen = Vec16<T>::kLen;
+    constexpr int G = 32 / L;    // lane groups; a group takes at most 32 / G = L nonzeros
+    constexpr int kAlign = 4;    // vec_len of the preprocessing
+    constexpr int kBlockK = 32;  // k_block of the preprocessing
+    constexpr unsigned kFull = 0xffffffffu;
+    const int item = blockIdx.x * kSmallGridWarps + (threadIdx.x >> 5);
+    if (item >= m2) return;
+    const int lane = threadIdx.x & 31;
+    const int g = lane / L, l = lane % L;
+
+    const int row = __ldg(residue_r_ind + item);
+    const int begin = __ldg(row_offsets + row);
+    const int end = __ldg(row_offsets + row + 1);
+    if (end - begin + (begin % kAlign) >= kBlockK) return;  // the block part took this row's tail
+    const int len = end - begin;                            // < 32
+
+    int c = 0;
+    T val = T(0);
+    if (lane < len) {
+        c = ld_stream(column_indices + begin + lane);
+        val = ld_stream(values + begin + lane);
+    }
+    const size_t row_vecs = static_cast<size_t>(n) / kLen;
+    const size_t col_vec = static_cast<size_t>(blockIdx.y) * L * VPL + l;
+    const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
+
+    int cc[L];
+    T vv[L];
+    V bb[L][VPL];
+#pragma unroll
+    for (int t = 0; t < L; ++t) {  // nonzero t * G + g
+        cc[t] = __shfl_sync(kFull, c, t * G + g);
+        vv[t] = __shfl_sync(kFull, val, t * G + g);
+    }
+#pragma unroll
+    for (int t = 0; t < L; ++t)
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            bb[t][v] = vzero(static_cast<V *>(nullptr));
+            if (t * G + g < len) bb[t][v] = ld_dense(b_lane + static_cast<size_t>(cc[t]) * row_vecs + v * L);
+        }
+    V acc[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+        acc[v] = vzero(static_cast<V *>(nullptr));
+#pragma unroll
+        for (int t = 0; t < L; ++t) vfma(acc[v], vv[t], bb[t][v]);
+#pragma unroll
+        for (int d = L; d < 32; d <<= 1) vadd(acc[v], vshfl_xor(kFull, acc[v], d));
+    }
+    if (g == 0) {
+#pragma unroll
+        for (int v = 0; v < VPL; ++v)
+            st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec + v * L, acc[v]);
+    }
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;
@@ -499,15 +590,18 @@ int launch_shape(int m1, int m2, int n, const T *values, const int *col, const i
     constexpr int USmall = (kChunkSteps * VPL <= 32) ? kChunkSteps : 32 / VPL;  // small grids
     const unsigned tiles = static_cast<unsigned>(n / kTileWidth);
     if (m1 > 0) {
-        dim3 grid((m1 + kCtaWarps - 1) / kCtaWarps, tiles);
-        // fewer warps than two full waves of 32 per SM: latency of the longest segment rules
+        // Fewer warps than two full waves of 32 per SM: the latency of the longest segment
+        // rules, so batches are larger.  CTAs stay one warp: with 4-warp CTAs the Zipf matrix
+        // (segments of 32 to 512 nonzeros side by side) ran 0.035 ms instead of 0.029 ms at
+        // N = 32 and 0.27 ms instead of 0.06 ms at N = 128.
         const bool small_grid = static_cast<long long>(m1) * tiles <= 2LL * 32 * sm_count();
+        dim3 grid((m1 + kCtaWarps - 1) / kCtaWarps, tiles);
         if (small_grid && USmall > U)
-            spmm_block<T, L, VPL, USmall><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets,
-                                                                        block_r_ind, st_off, B, C, partial);
+            spmm_block<T, L, VPL, USmall, kCtaWarps><<<grid, kCtaThreads, 0, s1>>>(
+                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial);
         else
-            spmm_block<T, L, VPL, U><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets, block_r_ind,
-                                                                   st_off, B, C, partial);
+            spmm_block<T, L, VPL, U, kCtaWarps><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets,
+                                                                              block_r_ind, st_off, B, C, partial);
         RODE_CHECK_LAUNCH("rode::spmm_block");
         // fix-up as a programmatic dependent of spmm_block: its launch latency and its
         // metadata prologue overlap the tail of the block grid
@@ -547,6 +641,9 @@ int launch_rows(int m2, int n, const T *values, const int *col, const int *row_o
             dim3 grid(static_cast<unsigned>((groups + kGroupsPerCta - 1) / kGroupsPerCta), tiles);
             spmm_rows<T, 32><<<grid, kCtaThreads, 0, s2>>>(m2, per_group, n, values, col, row_offsets,
                                                            residue_r_ind, B, C);
+        } else if (static_cast<long long>(m2) * tiles <= RODE_SPMM_WIDE_ROWS_WAVES * 32LL * sm_count()) {
+            dim3 grid((m2 + kSmallGridWarps - 1) / kSmallGridWarps, tiles);
+            spmm_rows_wide<T, L, VPL><<<grid, 32 * kSmallGridWarps, 0, s2>>>(m2, n, values, col, row_offsets, residue_r_ind, B, C);
         } else {
             constexpr int kRowsPerCta = kRowsCtaThreads / L;
             dim3 grid((m2 + kRowsPerCta - 1) / kRowsPerCta, tiles);
