@@ -26,35 +26,67 @@ int fail(int status, const char *fmt, ...) {
 
 namespace {
 
-// One growable scratch buffer per device and purpose, owned by the library for callers of
-// the reference-signature entry points, which carry no workspace argument.  Growing frees
-// the old buffer with cudaFree, which waits for work that may still use it.
-struct DeviceScratch {
+// Scratch buffers owned by the library for callers of the reference-signature entry points,
+// which carry no workspace argument.  One growable buffer per (purpose, device, stream): calls
+// on the same stream are ordered by the stream, so they may share a buffer; calls on different
+// streams may overlap on the GPU and get buffers of their own, which keeps the entry points
+// re-entrant like the reference's.  At most kMaxScratch buffers are kept; the least recently
+// used one is released when a new key arrives.  Growing or releasing calls cudaFree, which
+// waits for work that may still use the buffer.
+struct Scratch {
+    int kind = 0;
+    int dev = -1;
+    cudaStream_t stream = nullptr;
     void *ptr = nullptr;
     size_t bytes = 0;
+    unsigned long long last_use = 0;
 };
-constexpr int kMaxDevices = 64;
-enum ScratchKind { kSpmmScratch = 0, kPreprocessScratch = 1, kScratchKinds = 2 };
-DeviceScratch g_scratch[kScratchKinds][kMaxDevices];
+constexpr int kMaxScratch = 32;
+enum ScratchKind { kSpmmScratch = 0, kPreprocessScratch = 1 };
+Scratch g_scratch[kMaxScratch];
+unsigned long long g_scratch_clock = 0;
 std::mutex g_scratch_mutex;
 
-int scratch_for(ScratchKind kind, size_t bytes, void **out) {
+int scratch_for(ScratchKind kind, cudaStream_t stream, size_t bytes, void **out) {
     *out = nullptr;
     if (bytes == 0) return RODE_OK;
     int dev = 0;
     RODE_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDevices) return fail(RODE_ERR_NO_DEVICE, "device index %d out of range", dev);
     std::lock_guard<std::mutex> lock(g_scratch_mutex);
-    DeviceScratch &s = g_scratch[kind][dev];
-    if (s.bytes < bytes) {
-        if (s.ptr) RODE_CUDA_TRY(cudaFree(s.ptr));
-        s.ptr = nullptr;
-        s.bytes = 0;
-        const size_t grown = bytes + bytes / 4;  // head-room against repeated regrowth
-        RODE_CUDA_TRY(cudaMalloc(&s.ptr, grown));
-        s.bytes = grown;
+    Scratch *slot = nullptr, *oldest = &g_scratch[0];
+    for (Scratch &s : g_scratch) {
+        if (s.ptr && s.kind == kind && s.dev == dev && s.stream == stream) {
+            slot = &s;
+            break;
+        }
+        if (s.ptr == nullptr ? oldest->ptr != nullptr : (oldest->ptr != nullptr && s.last_use < oldest->last_use))
+            oldest = &s;  // a free slot wins over any used one; among used ones the oldest
     }
-    *out = s.ptr;
+    if (slot == nullptr) {
+        slot = oldest;
+        if (slot->ptr) {  // evict: the buffer belongs to another device if slot->dev != dev
+            int err = cudaSuccess;
+            if (slot->dev != dev) err = cudaSetDevice(slot->dev);
+            if (err == cudaSuccess) err = cudaFree(slot->ptr);
+            if (slot->dev != dev) cudaSetDevice(dev);
+            if (err != cudaSuccess)
+                return fail(RODE_ERR_CUDA, "scratch: cudaFree failed: %s", cudaGetErrorString(static_cast<cudaError_t>(err)));
+        }
+        *slot = Scratch();
+        slot->kind = kind;
+        slot->dev = dev;
+        slot->stream = stream;
+    }
+    if (slot->bytes < bytes) {
+        if (slot->ptr) RODE_CUDA_TRY(cudaFree(slot->ptr));
+        slot->ptr = nullptr;
+        slot->bytes = 0;
+        const size_t grown = bytes + bytes / 4;  // head-room against repeated regrowth
+        RODE_CUDA_TRY(cudaMalloc(&slot->ptr, grown));
+        slot->bytes = grown;
+    }
+    slot->last_use = ++g_scratch_clock;
+    *out = slot->ptr;
     return RODE_OK;
 }
 
@@ -69,7 +101,7 @@ void spmm_entry(int tile, int m1, int m2, int k, int n, const T *values, const i
     size_t need = 0;
     if (rode_spmm_workspace_bytes(m1, n, static_cast<int>(sizeof(T)), &need) != RODE_OK) return;
     void *ws = nullptr;
-    if (scratch_for(kSpmmScratch, need, &ws) != RODE_OK) return;
+    if (scratch_for(kSpmmScratch, s1, need, &ws) != RODE_OK) return;
     if (sizeof(T) == 4)
         rode_spmm_f32(m1, m2, k, n, reinterpret_cast<const float *>(values), col, row_offsets, blk, res, st,
                       reinterpret_cast<const float *>(B), reinterpret_cast<float *>(C), ws, need, s1, s2);
@@ -169,7 +201,7 @@ void RoDe_preprocess(int N_SEG, int blockX, int vecLen, int M, const int *row_pt
     size_t need = 0;
     if (rode_preprocess_workspace_bytes(M, &need) != RODE_OK) return;
     void *ws = nullptr;
-    if (rode::scratch_for(rode::kPreprocessScratch, need, &ws) != RODE_OK) return;
+    if (rode::scratch_for(rode::kPreprocessScratch, nullptr, need, &ws) != RODE_OK) return;
     rode_preprocess(N_SEG, blockX, vecLen, M, row_ptr, block_r_ind, st_off, residue_r_ind, n_blk, n_res, ws, need,
                     nullptr);
 }

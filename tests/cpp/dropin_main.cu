@@ -106,13 +106,28 @@ int main() {
     CHECK(cudaStreamCreate(&s2));
     RoDeSDDMM_n32(m1, m2, ncols, width, d_blk, d_res, d_st, d_rp, d_col, d_val, d_lhs, d_rhs, d_out, s1, s2);
     RoDeSpmm_n32(m1, m2, ncols, width, d_val, d_col, d_rp, d_blk, d_res, d_st, d_rhs, d_C, s1, s2);
+    // a second SpMM on streams of its own, in flight together with the first: the entry points
+    // keep no state that two concurrent calls could share (split rows use library scratch)
+    cudaStream_t s3, s4;
+    float *d_C2 = nullptr;
+    CHECK(cudaStreamCreate(&s3));
+    CHECK(cudaStreamCreate(&s4));
+    CHECK(cudaMalloc(&d_C2, sizeof(float) * m * width));
+    CHECK(cudaMemset(d_C2, 0, sizeof(float) * m * width));
+    RoDeSpmm_n32(m1, m2, ncols, width, d_val, d_col, d_rp, d_blk, d_res, d_st, d_rhs, d_C2, s3, s4);
     CHECK(cudaStreamSynchronize(s1));
     CHECK(cudaStreamSynchronize(s2));
+    CHECK(cudaStreamSynchronize(s3));
+    CHECK(cudaStreamSynchronize(s4));
     CHECK(cudaGetLastError());
 
     std::vector<float> out(nnz), C(static_cast<size_t>(m) * width);
     CHECK(cudaMemcpy(out.data(), d_out, sizeof(float) * nnz, cudaMemcpyDeviceToHost));
     CHECK(cudaMemcpy(C.data(), d_C, sizeof(float) * m * width, cudaMemcpyDeviceToHost));
+    std::vector<float> C2(C.size());
+    CHECK(cudaMemcpy(C2.data(), d_C2, sizeof(float) * m * width, cudaMemcpyDeviceToHost));
+    bool concurrent_same = true;
+    for (size_t i = 0; i < C.size() && concurrent_same; ++i) concurrent_same = C[i] == C2[i];
     double worst_sddmm = 0.0, worst_spmm = 0.0;
     for (int i = 0; i < m; ++i) {
         std::vector<double> acc(width, 0.0);
@@ -124,8 +139,8 @@ int main() {
         }
         for (int k = 0; k < width; ++k) worst_spmm = std::fmax(worst_spmm, std::fabs(C[i * width + k] - acc[k]));
     }
-    const bool ok = same && worst_sddmm < 2e-5 && worst_spmm < 2e-4;
-    std::printf("%s preprocess_same=%d m1=%d m2=%d nnz=%d max_abs_err sddmm=%.3g spmm=%.3g\n", ok ? "PASS" : "FAIL",
-                same ? 1 : 0, m1, m2, nnz, worst_sddmm, worst_spmm);
+    const bool ok = same && concurrent_same && worst_sddmm < 2e-5 && worst_spmm < 2e-4;
+    std::printf("%s preprocess_same=%d concurrent_same=%d m1=%d m2=%d nnz=%d max_abs_err sddmm=%.3g spmm=%.3g\n",
+                ok ? "PASS" : "FAIL", same ? 1 : 0, concurrent_same ? 1 : 0, m1, m2, nnz, worst_sddmm, worst_spmm);
     return ok ? 0 : 1;
 }
