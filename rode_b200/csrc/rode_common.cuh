@@ -112,4 +112,17 @@ __device__ __forceinline__ unsigned group_mask(int lane) {
 
 #endif  // __CUDACC__
 
+// Number of SMs of the current device (looked up once per device; 148 if the query fails).
+inline int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cached[dev] = v;
+    }
+    return cached[dev];
+}
+
 }  // namespace rode

@@ -18,6 +18,7 @@
 //
 // HBM traffic: row_ptr is read twice (8 B/row), outputs written once (8 B/segment,
 // 4 B/residue row), scratch is 8 B per 1024 rows.
+#include <climits>
 #include <mutex>
 
 #include "rode_common.cuh"
@@ -31,19 +32,36 @@ constexpr int kTile = kThreads * kRowsPerThread;  // rows per CTA
 constexpr int kWarps = kThreads / 32;
 constexpr int kLongRow = 8;  // rows with more segments than this are written by a warp
 
+// The three parameters of the decomposition.  kPow2 = all of them are powers of two (every
+// parameter set the reference uses: (512, 32, 4) and (32, 32, 4)): quotients and remainders
+// are then shifts and masks.  With run-time divisors the five integer divisions per row made
+// the count and fill kernels instruction-bound (about 150 instructions per row).
+struct Params {
+    int seg_len, k_block, vec_len;
+    int seg_shift;  // log2(seg_len) when kPow2
+};
+template <bool kPow2>
+__device__ __forceinline__ int mod_vec(int x, const Params &p) {
+    return kPow2 ? (x & (p.vec_len - 1)) : (x % p.vec_len);
+}
+template <bool kPow2>
+__device__ __forceinline__ int mod_block(int x, const Params &p) {
+    return kPow2 ? (x & (p.k_block - 1)) : (x % p.k_block);
+}
+
 // Number of block segments and residue flag of one row (closed form of the spec loop;
 // valid because seg_len % k_block == 0).
-__device__ __forceinline__ void row_counts(int off, int next, int seg_len, int k_block, int vec_len,
-                                           int &bn, int &rn) {
-    const int pad = off % vec_len;
-    const int a = next - off + pad;
-    if (a > seg_len) {
-        const int rest = a % seg_len;
-        bn = a / seg_len + (rest >= k_block ? 1 : 0);
-        rn = (rest % k_block) != 0 ? 1 : 0;
+template <bool kPow2>
+__device__ __forceinline__ void row_counts(int off, int next, const Params &p, int &bn, int &rn) {
+    const int a = next - off + mod_vec<kPow2>(off, p);
+    if (a > p.seg_len) {
+        const int rest = kPow2 ? (a & (p.seg_len - 1)) : (a % p.seg_len);
+        const int full = kPow2 ? (a >> p.seg_shift) : (a / p.seg_len);
+        bn = full + (rest >= p.k_block ? 1 : 0);
+        rn = mod_block<kPow2>(rest, p) != 0 ? 1 : 0;
     } else {
-        bn = a >= k_block ? 1 : 0;
-        rn = (a % k_block) != 0 ? 1 : 0;
+        bn = a >= p.k_block ? 1 : 0;
+        rn = mod_block<kPow2>(a, p) != 0 ? 1 : 0;
     }
 }
 
@@ -86,9 +104,9 @@ __device__ __forceinline__ void block_exclusive_scan2(int x, int y, int *smem, i
     __syncthreads();
 }
 
+template <bool kPow2>
 __global__ void __launch_bounds__(kThreads)
-count_tiles(int seg_len, int k_block, int vec_len, int M, const int *__restrict__ row_ptr,
-            int2 *__restrict__ tile_totals) {
+count_tiles(Params p, int M, const int *__restrict__ row_ptr, int2 *__restrict__ tile_totals) {
     __shared__ int smem[2 * kWarps];
     const int row0 = blockIdx.x * kTile + threadIdx.x * kRowsPerThread;
     int bsum = 0, rsum = 0;
@@ -99,7 +117,7 @@ count_tiles(int seg_len, int k_block, int vec_len, int M, const int *__restrict_
             if (row0 + i < M) {
                 const int next = row_ptr[row0 + i + 1];
                 int bn, rn;
-                row_counts(off, next, seg_len, k_block, vec_len, bn, rn);
+                row_counts<kPow2>(off, next, p, bn, rn);
                 bsum += bn;
                 rsum += rn;
                 off = next;
@@ -136,10 +154,10 @@ scan_tiles(int n_tiles, int M, const int *__restrict__ row_ptr, int2 *__restrict
     }
 }
 
+template <bool kPow2>
 __global__ void __launch_bounds__(kThreads)
-fill_tiles(int seg_len, int k_block, int vec_len, int M, const int *__restrict__ row_ptr,
-           const int2 *__restrict__ tile_offsets, int *__restrict__ block_r_ind, int *__restrict__ st_off,
-           int *__restrict__ residue_r_ind) {
+fill_tiles(Params p, int M, const int *__restrict__ row_ptr, const int2 *__restrict__ tile_offsets,
+           int *__restrict__ block_r_ind, int *__restrict__ st_off, int *__restrict__ residue_r_ind) {
     __shared__ int smem[2 * kWarps];
     // Long rows of this tile, written cooperatively after the per-thread pass.
     __shared__ int long_row[kTile];
@@ -163,7 +181,7 @@ fill_tiles(int seg_len, int k_block, int vec_len, int M, const int *__restrict__
         for (int i = 0; i < kRowsPerThread; ++i) {
             if (row0 + i < M) {
                 offs[i + 1] = row_ptr[row0 + i + 1];
-                row_counts(offs[i], offs[i + 1], seg_len, k_block, vec_len, bn[i], rn[i]);
+                row_counts<kPow2>(offs[i], offs[i + 1], p, bn[i], rn[i]);
                 bsum += bn[i];
                 rsum += rn[i];
             } else {
@@ -186,12 +204,12 @@ fill_tiles(int seg_len, int k_block, int vec_len, int M, const int *__restrict__
             long_cnt[slot] = bn[i];
         } else if (bn[i] > 0) {
             const int off = offs[i];
-            const int aligned = off - off % vec_len;
+            const int aligned = off - mod_vec<kPow2>(off, p);
             block_r_ind[gb] = row;
             st_off[gb] = off;
             for (int j = 1; j < bn[i]; ++j) {
                 block_r_ind[gb + j] = row;
-                st_off[gb + j] = aligned + j * seg_len;
+                st_off[gb + j] = aligned + j * p.seg_len;
             }
         }
         if (rn[i]) residue_r_ind[gr] = row;
@@ -205,10 +223,10 @@ fill_tiles(int seg_len, int k_block, int vec_len, int M, const int *__restrict__
     for (int s = warp; s < total_long; s += kWarps) {
         const int row = long_row[s], dst = long_dst[s], cnt = long_cnt[s];
         const int off = row_ptr[row];
-        const int aligned = off - off % vec_len;
+        const int aligned = off - mod_vec<kPow2>(off, p);
         for (int j = lane; j < cnt; j += 32) {
             block_r_ind[dst + j] = row;
-            st_off[dst + j] = j == 0 ? off : aligned + j * seg_len;
+            st_off[dst + j] = j == 0 ? off : aligned + j * p.seg_len;
         }
     }
 }
@@ -220,7 +238,8 @@ int check_params(int seg_len, int k_block, int vec_len, int M, const void *row_p
         return fail(RODE_ERR_INVALID_ARGUMENT,
                     "preprocess: need seg_len %% k_block == 0 and k_block %% vec_len == 0 (got %d, %d, %d)",
                     seg_len, k_block, vec_len);
-    if (M < 0) return fail(RODE_ERR_INVALID_ARGUMENT, "preprocess: M must be >= 0");
+    if (M < 0 || M > INT_MAX - kTile)
+        return fail(RODE_ERR_INVALID_ARGUMENT, "preprocess: M = %d outside [0, %d]", M, INT_MAX - kTile);
     if (row_ptr == nullptr) return fail(RODE_ERR_INVALID_ARGUMENT, "preprocess: row_ptr is null");
     return RODE_OK;
 }
@@ -232,15 +251,26 @@ int launch_preprocess(int seg_len, int k_block, int vec_len, int M, const int *r
                       int *st_off, int *residue_r_ind, int *n_blk, int *n_res, int2 *tile_scratch,
                       cudaStream_t stream) {
     const int n_tiles = (M + kTile - 1) / kTile;
+    auto pow2 = [](int x) { return (x & (x - 1)) == 0; };
+    const bool all_pow2 = pow2(seg_len) && pow2(k_block) && pow2(vec_len);
+    Params p = {seg_len, k_block, vec_len, 0};
+    while (all_pow2 && (1 << p.seg_shift) < seg_len) ++p.seg_shift;
     if (n_tiles > 0) {
-        count_tiles<<<n_tiles, kThreads, 0, stream>>>(seg_len, k_block, vec_len, M, row_ptr, tile_scratch);
+        if (all_pow2)
+            count_tiles<true><<<n_tiles, kThreads, 0, stream>>>(p, M, row_ptr, tile_scratch);
+        else
+            count_tiles<false><<<n_tiles, kThreads, 0, stream>>>(p, M, row_ptr, tile_scratch);
         RODE_CHECK_LAUNCH("rode::count_tiles");
     }
     scan_tiles<<<1, kScanThreads, 0, stream>>>(n_tiles, M, row_ptr, tile_scratch, st_off, n_blk, n_res);
     RODE_CHECK_LAUNCH("rode::scan_tiles");
     if (n_tiles > 0) {
-        fill_tiles<<<n_tiles, kThreads, 0, stream>>>(seg_len, k_block, vec_len, M, row_ptr, tile_scratch,
-                                                     block_r_ind, st_off, residue_r_ind);
+        if (all_pow2)
+            fill_tiles<true><<<n_tiles, kThreads, 0, stream>>>(p, M, row_ptr, tile_scratch, block_r_ind, st_off,
+                                                               residue_r_ind);
+        else
+            fill_tiles<false><<<n_tiles, kThreads, 0, stream>>>(p, M, row_ptr, tile_scratch, block_r_ind, st_off,
+                                                                residue_r_ind);
         RODE_CHECK_LAUNCH("rode::fill_tiles");
     }
     return RODE_OK;

@@ -337,18 +337,6 @@ sddmm_block(int m1, const int *__restrict__ block_r_ind, const int *__restrict__
     }
 }
 
-int sm_count() {
-    static int cached[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int v = 0;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
-        cached[dev] = v;
-    }
-    return cached[dev];
-}
-
 // Items per warp: 32 when that still gives every SM several waves of warps, fewer otherwise.
 int items_per_warp(int n_items, int cap) {
     const long long slots = 4LL * 24 * sm_count();

@@ -563,18 +563,6 @@ spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restric
     }
 }
 
-int sm_count() {
-    static int cached[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int v = 0;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
-        cached[dev] = v;
-    }
-    return cached[dev];
-}
-
 template <typename T, int L, int VPL>
 int launch_rows(int m2, int n, const T *values, const int *col, const int *row_offsets, const int *residue_r_ind,
                 const T *B, T *C, cudaStream_t s2);
