@@ -62,6 +62,16 @@ def test_gpu_preprocess_tile_boundaries_and_long_rows(oracle_cpu):
             _same(_gpu(rp, seg, kb, vec), oracle_cpu.preprocess(rp, seg, kb, vec))
 
 
+def test_gpu_preprocess_more_tiles_than_one_scan_pass(oracle_cpu):
+    """More than 8192 tiles of 1024 rows: the single-CTA tile scan needs a second pass."""
+    rng = np.random.default_rng(6)
+    m = 8192 * 1024 + 5000
+    lens = rng.integers(0, 40, m)
+    lens[rng.integers(0, m, 50)] = 3000
+    rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    _same(_gpu(rp, 512, 32, 4), oracle_cpu.preprocess(rp, 512, 32, 4))
+
+
 def test_reference_signature_entry_point(oracle_cpu):
     """RoDe_preprocess(N_SEG, blockX, vecLen, M, device pointers...) as the reference declares it."""
     lib = capi.load()
