@@ -129,8 +129,12 @@ int rode_preprocess_cpu(int seg_len, int k_block, int vec_len, int M, const int 
  * at an aligned offset), exactly the rows the reference never touches.
  *
  * Rows split over several segments are summed through `workspace`
- * (rode_spmm_workspace_bytes(m1, n, sizeof(T)) bytes, 256-byte aligned, may be null when
+ * (rode_spmm_workspace_bytes(m1, n, sizeof(T)) bytes, 16-byte aligned, may be null when
  * that size is 0).  Column byte offsets are formed in 64 bits.
+ *
+ * The metadata must come from the preprocessing with k_block = 32 and vec_len = 4 (any
+ * seg_len that is a multiple of 32), the values the reference's kernels are written for
+ * (RoDe_SpMM/RoDeSpmm.cu:513,518: 4-wide vectors, 32-nonzero tiles); st_off[m1] is not read.
  */
 int rode_spmm_workspace_bytes(int m1, int n, int elem_size, size_t *bytes);
 
@@ -152,7 +156,8 @@ int rode_spmm_f64(int m1, int m2, int k, int n, const double *values, const int 
  * lhs is [M x k], rhs is [n x k], both row-major; out is fp32[nnz] aligned with values.
  * Block segments run on stream1, pure-residue rows on stream2.  A null stream is the
  * default stream (the reference silently skips a kernel whose stream handle is null,
- * RoDeSddmm.cu:503,509; this library does not).  Needs no workspace.
+ * RoDeSddmm.cu:503,509; this library does not).  Needs no workspace.  Metadata as for SpMM:
+ * k_block = 32, vec_len = 4, any seg_len that is a multiple of 32.
  */
 int rode_sddmm_f32(int m1, int m2, int n, int k, const int *block_r_ind, const int *residue_r_ind,
                    const int *st_off, const int *row_offsets, const int *column_indices,
