@@ -48,7 +48,12 @@ def _f32(a) -> np.ndarray:
 
 
 def max_threads() -> int:
-    return int(lib().rode_oracle_max_threads())
+    """Host threads this process may run on.  Not OpenMP's own default: launchers such as
+    torchrun export OMP_NUM_THREADS=1, and the functions here take the count explicitly."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:  # platforms without sched_getaffinity
+        return max(1, os.cpu_count() or int(lib().rode_oracle_max_threads()))
 
 
 def preprocess_count(row_ptr, seg_len: int, k_block: int, vec_len: int):
