@@ -43,6 +43,8 @@ FALLBACK_HBM_GBS = 6650.0
 # `python bench.py --only spmm --family rmat --scale S --width 128 --steps 1 --warmup 1`
 # (summarised in profiles/spmm_dram_traffic_rmat23_n128.md).
 NCU_TRAFFIC_BYTES = {23: 27331223808 + 286452992, 21: 3849421824 + 93184512}
+# the same capture with the column popularity hints in use (default budget)
+NCU_TRAFFIC_BYTES_HINTS = {23: 22339756032 + 286452992}
 
 
 def parse_args():
@@ -56,6 +58,11 @@ def parse_args():
     p.add_argument("--e2e-steps", type=int, default=6)
     p.add_argument("--row-weight", type=float, default=2.0,
                    help="multi-GPU partition: cost of a row = its nnz + this (0 = plain nnz-balanced)")
+    p.add_argument("--hints", choices=["on", "off"], default="on",
+                   help="column popularity hints for the SpMM gathers (rode_hot_columns); on = use them where the "
+                        "library finds them useful")
+    p.add_argument("--hint-budget-mb", type=float, default=0.0,
+                   help="bytes of dense rows the hints may mark, in MB (0 = the library's default)")
     p.add_argument("--only", choices=["spmm", "sddmm"], default=None,
                    help="small single-op run (one family, one width) for profiling and A/B timing")
     p.add_argument("--family", default="rmat", choices=["bernoulli", "zipf", "stencil", "pareto", "rmat"])
@@ -206,6 +213,33 @@ def time_preprocess(row_ptr, nnz, seg, iters, peak_gbs, with_host=True):
         capi.preprocess_cpu(rp_host, seg, 32, 4)
         out["host_single_thread_ms"] = (time.perf_counter() - t0) * 1e3
     return out
+
+
+def time_hot_columns(col, n_cols, row_bytes, iters):
+    """Device time of the column-popularity pass (raw entry point, buffers allocated once) and
+    what it marked."""
+    import ctypes
+
+    import numpy as np
+    from rode_b200 import capi
+
+    dev = col.device
+    words, need = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    capi.check(capi.load().rode_hot_columns_words(n_cols, ctypes.byref(words)))
+    capi.check(capi.load().rode_hot_columns_workspace_bytes(n_cols, ctypes.byref(need)))
+    bitmap = torch.empty(words.value, dtype=torch.int32, device=dev)
+    ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def run():
+        capi.hot_columns_raw(col.numel(), n_cols, col.data_ptr(), row_bytes, 0, bitmap.data_ptr(), ws.data_ptr(),
+                             need.value, stream)
+
+    ms = time_loop(run, iters, 3, stream)
+    raw = bitmap.cpu().numpy().view(np.uint32)
+    marked = int(np.unpackbits(raw[:-1].view(np.uint8)).sum())
+    return {"gpu_ms": ms, "useful": bool(raw[-1]), "marked_columns": marked, "marked_bytes": marked * row_bytes,
+            "budget": "60 % of the device's L2"}
 
 
 class ForkJoin:
@@ -435,11 +469,15 @@ def single_op(args):
         C = torch.zeros((A.m, width), device=dev)
         need = capi.spmm_workspace_bytes(meta.m1, width, 4)
         ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        hot = (capi.hot_columns(A.col, A.n, 4 * width, budget_bytes=int(args.hint_budget_mb * 1e6))
+               if args.hints == "on" else None)
+        hot_ptr = None if hot is None else hot.data_ptr()
 
         def launch(s1, s2):
             capi.spmm_raw(torch.float32, meta.m1, meta.m2, A.n, width, A.val.data_ptr(), A.col.data_ptr(),
                           A.row_ptr.data_ptr(), meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(),
-                          meta.st_off.data_ptr(), B.data_ptr(), C.data_ptr(), ws.data_ptr(), need, s1, s2)
+                          meta.st_off.data_ptr(), B.data_ptr(), C.data_ptr(), ws.data_ptr(), need, s1, s2,
+                          hot=hot_ptr)
 
         bmin = spmm_bmin(A.nnz, A.m, width, k_touched)
     else:
@@ -456,6 +494,7 @@ def single_op(args):
     flush = torch.zeros(64 * 1024 * 1024, device=dev)
     ms = time_loop(lambda: fj.run(launch), args.steps, args.warmup, fj.cur, flush)
     return {"only": args.only, "family": args.family, "width": width, "rows": A.m, "nnz": A.nnz,
+            "hints": bool(args.only == "spmm" and hot is not None),
             "m1": meta.m1, "m2": meta.m2, "ms": ms, "gflops": 2.0 * A.nnz * width / ms / 1e6,
             "bmin_bytes": bmin, "algorithmic_gbs": bmin / ms / 1e6,
             "frac": bmin / ms / 1e6 / peak_gbs, "peak_kind": peak_kind, "k_touched": k_touched}
@@ -574,13 +613,20 @@ def main():
     ws_bytes = capi.spmm_workspace_bytes(meta.m1, N_DENSE, 4)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
     fj = ForkJoin(dev)
+    # column popularity bitmap of this rank's rows (set-up, like the preprocessing; timed below)
+    hot = (capi.hot_columns(mine.col, n_vert, 4 * N_DENSE, budget_bytes=int(args.hint_budget_mb * 1e6))
+           if args.hints == "on" else None)
+    hot_ptr = None if hot is None else hot.data_ptr()
+    hints_info = {"requested": args.hints == "on", "used": hot is not None}
+    if args.hints == "on":
+        hints_info.update(time_hot_columns(mine.col, n_vert, 4 * N_DENSE, 10))
     setup_s = time.perf_counter() - t_setup
 
     def spmm_launch(s1, s2, m1=None, m2=None):
         capi.spmm_raw(torch.float32, meta.m1 if m1 is None else m1, meta.m2 if m2 is None else m2, n_vert, N_DENSE,
                       mine.val.data_ptr(), mine.col.data_ptr(), mine.row_ptr.data_ptr(), meta.block_r_ind.data_ptr(),
                       meta.residue_r_ind.data_ptr(), meta.st_off.data_ptr(), X.data_ptr(), C.data_ptr(),
-                      ws.data_ptr(), ws_bytes, s1, s2)
+                      ws.data_ptr(), ws_bytes, s1, s2, hot=hot_ptr)
 
     def step():
         fj.run(spmm_launch)
@@ -621,7 +667,8 @@ def main():
     block_bytes_all = sum_over_ranks(float(block_bytes))
     step_bytes_all = sum_over_ranks(float(spmm_bmin(my_nnz, my_rows, N_DENSE, kt_all)))
     roofline = {
-        "kernel": "rode::spmm_block<float,32> (timed with spmm_fixup, which follows it on the same stream)",
+        "kernel": ("rode::spmm_block<float,32> (timed with spmm_fixup, which follows it on the same stream)"
+                   + ("; dense rows of popular columns gathered with L2 evict_last" if hot is not None else "")),
         "bound": "hbm", "achieved": block_bytes_all / world / ms_block / 1e6 if ms_block else None,
         "peak": peak_gbs, "unit": "GB/s", "peak_kind": f"of {peak_kind}",
         "frac": (block_bytes_all / world / ms_block / 1e6 / peak_gbs) if ms_block else None,
@@ -635,9 +682,12 @@ def main():
         "step": {"algorithmic_bytes": step_bytes_all, "achieved": step_bytes_all / ms_step / 1e6,
                  "frac": step_bytes_all / ms_step / 1e6 / (peak_gbs * world)},
     }
-    if world == 1 and args.scale in NCU_TRAFFIC_BYTES:
-        roofline["traffic"] = NCU_TRAFFIC_BYTES[args.scale]
-        roofline["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one spmm_block launch on this workload"
+    traffic_table = NCU_TRAFFIC_BYTES_HINTS if hot is not None else NCU_TRAFFIC_BYTES
+    if world == 1 and args.scale in traffic_table and not args.hint_budget_mb:
+        roofline["traffic"] = traffic_table[args.scale]
+        roofline["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one spmm_block launch on "
+                                      "this workload" + (", popularity hints in use" if hot is not None else ""))
+        roofline["traffic_gbs"] = traffic_table[args.scale] / ms_block / 1e6 if ms_block else None
 
     # ---- SDDMM K = 64 on the same rows ---------------------------------------------------------
     lhs = W.dense(n_vert, K_SDDMM, device=dev, seed=5)[r0:r1].contiguous()
@@ -701,12 +751,16 @@ def main():
             dist.all_gather_into_tensor(d_X_full, bf["X"])
         dense_x = d_X_full if world > 1 else bf["X"]
         m = capi.preprocess(bf["rp"], my_nnz, 512, 32, 4)   # device-side row decomposition (reads 2 counts back)
+        # the matrix arrived with this step, so its popularity bitmap is built in this step too
+        h = (capi.hot_columns(bf["col"], n_vert, 4 * N_DENSE, budget_bytes=int(args.hint_budget_mb * 1e6))
+             if args.hints == "on" else None)
         bf["C"].zero_()                                       # the API's contract: C arrives zero-filled
 
         def launch(s1, s2):
             capi.spmm_raw(torch.float32, m.m1, m.m2, n_vert, N_DENSE, bf["val"].data_ptr(), bf["col"].data_ptr(),
                           bf["rp"].data_ptr(), m.block_r_ind.data_ptr(), m.residue_r_ind.data_ptr(),
-                          m.st_off.data_ptr(), dense_x.data_ptr(), bf["C"].data_ptr(), ws.data_ptr(), ws_bytes, s1, s2)
+                          m.st_off.data_ptr(), dense_x.data_ptr(), bf["C"].data_ptr(), ws.data_ptr(), ws_bytes, s1, s2,
+                          hot=None if h is None else h.data_ptr())
 
         fj.run(launch)
         bf["in_free"].record(fj.cur)
@@ -782,7 +836,7 @@ def main():
                        "l2": "inputs larger than L2 (dense operand 4.3 GB, CSR 1 GB); no flush between steps",
                        "m1_rank0": meta.m1, "m2_rank0": meta.m2},
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps, "nnz_per_s": nnz / ms_step * 1e3,
-            "roofline": roofline, "e2e": e2e, "sddmm": sddmm, "preprocess": preprocess_info,
+            "roofline": roofline, "e2e": e2e, "sddmm": sddmm, "preprocess": preprocess_info, "hints": hints_info,
             "cpu_baseline": cpu_baseline,
             "broadcast_ms": broadcast_ms, "setup_s": setup_s, "checksum": checksum,
         }

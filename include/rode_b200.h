@@ -149,6 +149,44 @@ int rode_spmm_f64(int m1, int m2, int k, int n, const double *values, const int 
                   size_t workspace_bytes, rode_stream_t stream1, rode_stream_t stream2);
 
 /* ------------------------------------------------------------------------------------
+ * Column popularity hints for the gathers.  No counterpart in the reference.
+ *
+ * When the dense operand is many times larger than the L2 and a few columns receive most of
+ * the references (power-law graphs), rows that are gathered once push rows that are gathered
+ * thousands of times out of the L2.  rode_hot_columns counts the references of every column
+ * and marks the most referenced ones whose dense rows (dense_row_bytes each) fit
+ * budget_bytes (0 = 60 % of the device's L2).  rode_spmm_f32_hot / _f64_hot then gather
+ * marked rows with the L2 policy evict_last and all others with evict_first.  Results are
+ * bit-identical to rode_spmm_f32 / _f64; only the DRAM traffic changes.
+ *
+ * hot_columns: unsigned[rode_hot_columns_words(n_cols)] = one bit per column plus a trailing
+ * flag word.  The flag is 0 when the marks would not help (the touched rows nearly fit the
+ * budget anyway, or the marked columns get less than twice their share of the references);
+ * the SpMM entry points must then be given a null hot_columns pointer, or simply the plain
+ * entry points be used.  The hints take effect for n that is a multiple of 128 (float) or
+ * 64 (double) and grids of more than two waves of warps; other calls ignore them.
+ * workspace: rode_hot_columns_workspace_bytes(n_cols) bytes, 256-byte aligned, only used
+ * during the call.
+ */
+int rode_hot_columns_workspace_bytes(int n_cols, size_t *bytes);
+int rode_hot_columns_words(int n_cols, size_t *words);
+int rode_hot_columns(long long nnz, int n_cols, const int *column_indices, size_t dense_row_bytes,
+                     size_t budget_bytes, unsigned *hot_columns, void *workspace,
+                     size_t workspace_bytes, rode_stream_t stream);
+
+int rode_spmm_f32_hot(int m1, int m2, int k, int n, const float *values, const int *column_indices,
+                      const int *row_offsets, const int *block_r_ind, const int *residue_r_ind,
+                      const int *st_off, const float *B, float *C, void *workspace,
+                      size_t workspace_bytes, const unsigned *hot_columns, rode_stream_t stream1,
+                      rode_stream_t stream2);
+
+int rode_spmm_f64_hot(int m1, int m2, int k, int n, const double *values, const int *column_indices,
+                      const int *row_offsets, const int *block_r_ind, const int *residue_r_ind,
+                      const int *st_off, const double *B, double *C, void *workspace,
+                      size_t workspace_bytes, const unsigned *hot_columns, rode_stream_t stream1,
+                      rode_stream_t stream2);
+
+/* ------------------------------------------------------------------------------------
  * SDDMM:  out[e] = values[e] * dot(lhs[row(e), 0:k], rhs[col(e), 0:k]) for every stored e.
  *
  * Replaces RoDeSDDMM_n32 / RoDeSDDMM_n128 (RoDe_SDDMM/RoDeSddmm.h:4-9, launchers

@@ -17,7 +17,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 LIB = os.path.join(PKG, "librode_b200.so")
-SOURCES = ["rode_host.cu", "rode_preprocess.cu", "rode_spmm.cu", "rode_sddmm.cu"]
+SOURCES = ["rode_host.cu", "rode_preprocess.cu", "rode_hot_columns.cu", "rode_spmm.cu", "rode_sddmm.cu"]
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr",

@@ -26,7 +26,8 @@ RODE_ERR_NO_DEVICE = 4
 C_ABI_SYMBOLS = (
     "rode_last_error", "rode_version", "rode_preprocess_workspace_bytes", "rode_preprocess_capacity",
     "rode_preprocess", "rode_preprocess_noalloc", "rode_preprocess_cpu", "rode_spmm_workspace_bytes", "rode_spmm_f32", "rode_spmm_f64",
-    "rode_sddmm_f32",
+    "rode_sddmm_f32", "rode_hot_columns_workspace_bytes", "rode_hot_columns_words", "rode_hot_columns",
+    "rode_spmm_f32_hot", "rode_spmm_f64_hot",
 )
 # Itanium-ABI names of the C++ entry points declared in RoDeSpmm.h / RoDeSddmm.h /
 # RoDePreprocess.h; identical to the names the reference's own objects export.
@@ -75,9 +76,15 @@ def load() -> ctypes.CDLL:
     lib.rode_spmm_f32.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp, vp]
     lib.rode_spmm_f64.argtypes = lib.rode_spmm_f32.argtypes
     lib.rode_sddmm_f32.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.rode_hot_columns_workspace_bytes.argtypes = [ci, ctypes.POINTER(sz)]
+    lib.rode_hot_columns_words.argtypes = [ci, ctypes.POINTER(sz)]
+    lib.rode_hot_columns.argtypes = [ctypes.c_longlong, ci, vp, sz, sz, vp, vp, sz, vp]
+    lib.rode_spmm_f32_hot.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp, vp, vp]
+    lib.rode_spmm_f64_hot.argtypes = lib.rode_spmm_f32_hot.argtypes
     for name in ("rode_preprocess_workspace_bytes", "rode_preprocess_capacity", "rode_preprocess",
                  "rode_preprocess_noalloc", "rode_preprocess_cpu", "rode_spmm_workspace_bytes", "rode_spmm_f32", "rode_spmm_f64",
-                 "rode_sddmm_f32"):
+                 "rode_sddmm_f32", "rode_hot_columns_workspace_bytes", "rode_hot_columns_words", "rode_hot_columns",
+                 "rode_spmm_f32_hot", "rode_spmm_f64_hot"):
         getattr(lib, name).restype = ci
     _lib = lib
     return lib
@@ -217,17 +224,53 @@ def spmm_workspace_bytes(m1: int, n: int, elem_size: int = 4) -> int:
 
 
 def spmm_raw(dtype, m1, m2, k, n, values, col, row_ptr, blk, res, st, B, C, workspace, workspace_bytes,
-             stream1=None, stream2=None) -> None:
-    fn = load().rode_spmm_f32 if dtype == torch.float32 else load().rode_spmm_f64
-    check(fn(m1, m2, k, n, values, col, row_ptr, blk, res, st, B, C, workspace, workspace_bytes, _stream(stream1),
-             _stream(stream2)))
+             stream1=None, stream2=None, hot=None) -> None:
+    """rode_spmm_f32 / _f64 on raw device addresses; with ``hot`` (address of a popularity
+    bitmap from ``hot_columns``) the _hot entry points."""
+    if hot is None:
+        fn = load().rode_spmm_f32 if dtype == torch.float32 else load().rode_spmm_f64
+        check(fn(m1, m2, k, n, values, col, row_ptr, blk, res, st, B, C, workspace, workspace_bytes,
+                 _stream(stream1), _stream(stream2)))
+    else:
+        fn = load().rode_spmm_f32_hot if dtype == torch.float32 else load().rode_spmm_f64_hot
+        check(fn(m1, m2, k, n, values, col, row_ptr, blk, res, st, B, C, workspace, workspace_bytes, hot,
+                 _stream(stream1), _stream(stream2)))
+
+
+def hot_columns_raw(nnz, n_cols, col, dense_row_bytes, budget_bytes, bitmap, workspace, workspace_bytes,
+                    stream=None) -> None:
+    check(load().rode_hot_columns(nnz, n_cols, col, dense_row_bytes, budget_bytes, bitmap, workspace,
+                                  workspace_bytes, _stream(stream)))
+
+
+def hot_columns(col: torch.Tensor, n_cols: int, dense_row_bytes: int, budget_bytes: int = 0,
+                stream=None) -> Optional[torch.Tensor]:
+    """Popularity bitmap of the columns for ``spmm(..., hot=...)`` (rode_hot_columns), or None
+    when the library finds that marks would not help on this matrix.  Reads the flag word back
+    (4-byte D2H copy, synchronises the stream)."""
+    _dev_i32(col, "col")
+    dev = col.device
+    words, need = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    check(load().rode_hot_columns_words(n_cols, ctypes.byref(words)))
+    check(load().rode_hot_columns_workspace_bytes(n_cols, ctypes.byref(need)))
+    with torch.cuda.device(dev):
+        if stream is None:
+            stream = torch.cuda.current_stream(dev)
+        with torch.cuda.stream(stream) if isinstance(stream, torch.cuda.Stream) else _null():
+            bitmap = torch.empty(words.value, dtype=torch.int32, device=dev)
+            ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
+            hot_columns_raw(col.numel(), n_cols, col.data_ptr(), dense_row_bytes, budget_bytes, bitmap.data_ptr(),
+                            ws.data_ptr(), need.value, stream)
+            useful = int(bitmap[-1].item())
+    return bitmap if useful else None
 
 
 def spmm(meta: RodeMeta, row_ptr: torch.Tensor, col: torch.Tensor, values: torch.Tensor, B: torch.Tensor,
          C: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None, stream1=None,
-         stream2=None) -> torch.Tensor:
+         stream2=None, hot: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C = S @ B through rode_spmm_f32 / rode_spmm_f64.  Asynchronous on the two streams
-    (default: torch's current stream for both).  ``C`` defaults to a fresh zero tensor."""
+    (default: torch's current stream for both).  ``C`` defaults to a fresh zero tensor.
+    ``hot``: popularity bitmap from ``hot_columns`` (same results, fewer DRAM bytes)."""
     M = row_ptr.numel() - 1
     k, n = B.shape
     if values.dtype not in (torch.float32, torch.float64) or B.dtype != values.dtype:
@@ -247,7 +290,7 @@ def spmm(meta: RodeMeta, row_ptr: torch.Tensor, col: torch.Tensor, values: torch
         ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
         spmm_raw(B.dtype, meta.m1, meta.m2, k, n, values.data_ptr(), col.data_ptr(), row_ptr.data_ptr(),
                  meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(), meta.st_off.data_ptr(), B.data_ptr(),
-                 C.data_ptr(), _ptr(workspace), ws_bytes, s1, s2)
+                 C.data_ptr(), _ptr(workspace), ws_bytes, s1, s2, hot=_ptr(hot))
     return C
 
 

@@ -89,6 +89,46 @@ __device__ __forceinline__ V ld_dense(const V *p) {
     return __ldg(p);
 }
 
+// Gathers steered by column popularity (rode_hot_columns): rows of marked columns are loaded
+// with the L2 policy evict_last, all others with evict_first, so that rows touched once do
+// not push the popular rows out of the L2.  A column index carries its mark in bit 31.
+struct GatherPolicy {
+    unsigned long long hot, cold;
+};
+__device__ __forceinline__ GatherPolicy make_gather_policy() {
+    GatherPolicy p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p.hot));
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p.cold));
+    return p;
+}
+__device__ __forceinline__ float4 ld_dense_policy(const float4 *p, unsigned long long policy) {
+    float4 v;
+    asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+        : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+        : "l"(p), "l"(policy));
+    return v;
+}
+__device__ __forceinline__ double2 ld_dense_policy(const double2 *p, unsigned long long policy) {
+    double2 v;
+    asm("ld.global.nc.L2::cache_hint.v2.f64 {%0, %1}, [%2], %3;" : "=d"(v.x), "=d"(v.y) : "l"(p), "l"(policy));
+    return v;
+}
+// Word of the popularity bitmap that holds column c, and c with its mark moved into bit 31.
+__device__ __forceinline__ unsigned hot_word(const unsigned *hot, int c) { return __ldg(hot + (c >> 5)); }
+__device__ __forceinline__ int tag_hot(int c, unsigned word) {
+    return c | static_cast<int>(((word >> (c & 31)) & 1u) << 31);
+}
+// Gather of the dense-row vector of a column: plain read-only load, or steered by the mark.
+template <bool kHints, typename V>
+__device__ __forceinline__ V gather(const V *lane_base, int c, size_t row_vecs, const GatherPolicy &policy) {
+    if constexpr (kHints) {
+        return ld_dense_policy(lane_base + static_cast<size_t>(c & 0x7fffffff) * row_vecs,
+                               c < 0 ? policy.hot : policy.cold);
+    } else {
+        return ld_dense(lane_base + static_cast<size_t>(c) * row_vecs);
+    }
+}
+
 // Streaming read of CSR data (touched once): do not let it displace dense rows in L1.
 __device__ __forceinline__ int ld_stream(const int *p) { return __ldcs(p); }
 __device__ __forceinline__ float ld_stream(const float *p) { return __ldcs(p); }

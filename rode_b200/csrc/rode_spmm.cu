@@ -88,11 +88,16 @@ constexpr int kLoadsInFlight = 8;
 // rows per batch: kLoadsInFlight / VPL for grids that fill the GPU (64 registers keep 32
 // warps per SM resident); the whole chunk for small grids, where the time is the
 // dependent-batch chain of the longest segment and registers are free.
-template <typename T, int L, int VPL, int U, int W>
-__global__ void __launch_bounds__(32 * W, (U * VPL > kLoadsInFlight) ? 1 : 32 / W)
+// One-warp CTAs per SM that the register budget must allow, by 16-byte loads in flight per
+// lane: 8 -> 32 CTAs (64 registers), 12 -> 25 (80), 16 -> 20 (96), more -> no limit.
+constexpr int min_ctas_per_sm(int loads) { return loads <= 8 ? 32 : loads <= 12 ? 25 : loads <= 16 ? 20 : 1; }
+
+template <typename T, int L, int VPL, int U, int W, bool kHints>
+__global__ void __launch_bounds__(32 * W, min_ctas_per_sm(U * VPL) / W)
 spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
            const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
-           const int *__restrict__ st_off, const T *__restrict__ B, T *__restrict__ C, T *__restrict__ partial) {
+           const int *__restrict__ st_off, const T *__restrict__ B, T *__restrict__ C, T *__restrict__ partial,
+           const unsigned *__restrict__ hot) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
     constexpr int G = 32 / L;             // lane groups, each takes every G-th nonzero
@@ -132,6 +137,14 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
         c_nxt = ld_stream(column_indices + off + 32 + lane);
         v_nxt = ld_stream(values + off + 32 + lane);
     }
+    // With popularity hints a column index carries its mark in bit 31.  The bitmap word of a
+    // column is fetched one chunk after the column itself (which has arrived by then) and one
+    // chunk before the column is used, so the lookup adds no exposed latency after the first.
+    GatherPolicy policy = {};
+    if constexpr (kHints) {
+        policy = make_gather_policy();
+        c_cur = tag_hot(c_cur, hot_word(hot, c_cur));
+    }
 
     V acc[VPL];
 #pragma unroll
@@ -144,6 +157,8 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
             c_pre = ld_stream(column_indices + base + 64 + lane);
             v_pre = ld_stream(values + base + 64 + lane);
         }
+        unsigned w_nxt = 0;
+        if constexpr (kHints) w_nxt = hot_word(hot, c_nxt);
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
             if (b * U * G >= cnt) break;  // warp-uniform
@@ -157,7 +172,7 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
 #pragma unroll
                 for (int v = 0; v < VPL; ++v) {
                     buf[u][v] = vzero(static_cast<V *>(nullptr));
-                    if (t < cnt) buf[u][v] = ld_dense(b_lane + static_cast<size_t>(c) * row_vecs + v * L);
+                    if (t < cnt) buf[u][v] = gather<kHints>(b_lane + v * L, c, row_vecs, policy);
                 }
             }
 #pragma unroll
@@ -165,7 +180,7 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
 #pragma unroll
                 for (int v = 0; v < VPL; ++v) vfma(acc[v], vv[u], buf[u][v]);
         }
-        c_cur = c_nxt;
+        c_cur = kHints ? tag_hot(c_nxt, w_nxt) : c_nxt;
         v_cur = v_nxt;
         c_nxt = c_pre;
         v_nxt = v_pre;
@@ -570,7 +585,7 @@ int launch_rows(int m2, int n, const T *values, const int *col, const int *row_o
 template <typename T, int L, int VPL, int RL, int RVPL>
 int launch_shape(int m1, int m2, int n, const T *values, const int *col, const int *row_offsets,
                  const int *block_r_ind, const int *residue_r_ind, const int *st_off, const T *B, T *C,
-                 T *partial, cudaStream_t s1, cudaStream_t s2) {
+                 T *partial, const unsigned *hot, cudaStream_t s1, cudaStream_t s2) {
     static_assert(L * VPL == RL * RVPL, "block and residue kernels must cover the same tile");
     constexpr int kTileWidth = L * VPL * Vec16<T>::kLen;
     constexpr int U = kLoadsInFlight / VPL;                      // rows per batch, large grids
@@ -584,12 +599,25 @@ int launch_shape(int m1, int m2, int n, const T *values, const int *col, const i
         // N = 32 and 0.27 ms instead of 0.06 ms at N = 128.
         const bool small_grid = static_cast<long long>(m1) * tiles <= 2LL * 32 * sm_count();
         dim3 grid((m1 + kCtaWarps - 1) / kCtaWarps, tiles);
-        if (small_grid && USmall > U)
-            spmm_block<T, L, VPL, USmall, kCtaWarps><<<grid, kCtaThreads, 0, s1>>>(
-                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial);
-        else
-            spmm_block<T, L, VPL, U, kCtaWarps><<<grid, kCtaThreads, 0, s1>>>(m1, n, values, col, row_offsets,
-                                                                              block_r_ind, st_off, B, C, partial);
+        bool launched = false;
+        // Popularity hints: block kernel of the 32-lane shape only.  In the residue-row kernel
+        // the marks saved DRAM bytes (5.36 -> 4.79 GB on R-MAT scale 23) but the extra registers
+        // cost more time than that returned (1.41 -> 1.52 ms).
+        if constexpr (L == 32 && VPL == 1) {
+            if (hot && !small_grid) {
+                spmm_block<T, L, VPL, U, kCtaWarps, true><<<grid, kCtaThreads, 0, s1>>>(
+                    m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, hot);
+                launched = true;
+            }
+        }
+        if (launched) {
+        } else if (small_grid && USmall > U) {
+            spmm_block<T, L, VPL, USmall, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
+                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr);
+        } else {
+            spmm_block<T, L, VPL, U, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
+                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr);
+        }
         RODE_CHECK_LAUNCH("rode::spmm_block");
         // fix-up as a programmatic dependent of spmm_block: its launch latency and its
         // metadata prologue overlap the tail of the block grid
@@ -631,7 +659,8 @@ int launch_rows(int m2, int n, const T *values, const int *col, const int *row_o
                                                            residue_r_ind, B, C);
         } else if (static_cast<long long>(m2) * tiles <= RODE_SPMM_WIDE_ROWS_WAVES * 32LL * sm_count()) {
             dim3 grid((m2 + kSmallGridWarps - 1) / kSmallGridWarps, tiles);
-            spmm_rows_wide<T, L, VPL><<<grid, 32 * kSmallGridWarps, 0, s2>>>(m2, n, values, col, row_offsets, residue_r_ind, B, C);
+            spmm_rows_wide<T, L, VPL><<<grid, 32 * kSmallGridWarps, 0, s2>>>(m2, n, values, col, row_offsets,
+                                                                             residue_r_ind, B, C);
         } else {
             constexpr int kRowsPerCta = kRowsCtaThreads / L;
             dim3 grid((m2 + kRowsPerCta - 1) / kRowsPerCta, tiles);
@@ -646,7 +675,7 @@ int launch_rows(int m2, int n, const T *values, const int *col, const int *row_o
 template <typename T>
 int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const int *row_offsets,
          const int *block_r_ind, const int *residue_r_ind, const int *st_off, const T *B, T *C, void *workspace,
-         size_t workspace_bytes, rode_stream_t stream1, rode_stream_t stream2) {
+         size_t workspace_bytes, const unsigned *hot, rode_stream_t stream1, rode_stream_t stream2) {
     constexpr int kLen = Vec16<T>::kLen;
     (void)k;
     if (m1 < 0 || m2 < 0 || n <= 0) return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: m1, m2 >= 0 and n > 0 required");
@@ -672,7 +701,8 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
     // Widest tile (32, 16 or 8 vectors of 16 bytes) that divides the row.
 #define RODE_LAUNCH(shape, rows_shape)                                                                        \
     launch_shape<T, (shape) / 100, (shape) % 100, (rows_shape) / 100, (rows_shape) % 100>(                     \
-        m1, m2, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, stream1, stream2)
+        m1, m2, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, hot, stream1, \
+        stream2)
     const int vecs = n / kLen;
     if (vecs % 32 == 0 && RODE_SPMM_MAX_TILE_VECS >= 32) return RODE_LAUNCH(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32);
     if (vecs % 16 == 0) return RODE_LAUNCH(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16);
@@ -698,7 +728,15 @@ int rode_spmm_f32(int m1, int m2, int k, int n, const float *values, const int *
                   const float *B, float *C, void *workspace, size_t workspace_bytes, rode_stream_t stream1,
                   rode_stream_t stream2) {
     return rode::spmm<float>(m1, m2, k, n, values, column_indices, row_offsets, block_r_ind, residue_r_ind,
-                             st_off, B, C, workspace, workspace_bytes, stream1, stream2);
+                             st_off, B, C, workspace, workspace_bytes, nullptr, stream1, stream2);
+}
+
+int rode_spmm_f32_hot(int m1, int m2, int k, int n, const float *values, const int *column_indices,
+                      const int *row_offsets, const int *block_r_ind, const int *residue_r_ind, const int *st_off,
+                      const float *B, float *C, void *workspace, size_t workspace_bytes,
+                      const unsigned *hot_columns, rode_stream_t stream1, rode_stream_t stream2) {
+    return rode::spmm<float>(m1, m2, k, n, values, column_indices, row_offsets, block_r_ind, residue_r_ind,
+                             st_off, B, C, workspace, workspace_bytes, hot_columns, stream1, stream2);
 }
 
 int rode_spmm_f64(int m1, int m2, int k, int n, const double *values, const int *column_indices,
@@ -706,7 +744,15 @@ int rode_spmm_f64(int m1, int m2, int k, int n, const double *values, const int 
                   const double *B, double *C, void *workspace, size_t workspace_bytes, rode_stream_t stream1,
                   rode_stream_t stream2) {
     return rode::spmm<double>(m1, m2, k, n, values, column_indices, row_offsets, block_r_ind, residue_r_ind,
-                              st_off, B, C, workspace, workspace_bytes, stream1, stream2);
+                              st_off, B, C, workspace, workspace_bytes, nullptr, stream1, stream2);
+}
+
+int rode_spmm_f64_hot(int m1, int m2, int k, int n, const double *values, const int *column_indices,
+                      const int *row_offsets, const int *block_r_ind, const int *residue_r_ind, const int *st_off,
+                      const double *B, double *C, void *workspace, size_t workspace_bytes,
+                      const unsigned *hot_columns, rode_stream_t stream1, rode_stream_t stream2) {
+    return rode::spmm<double>(m1, m2, k, n, values, column_indices, row_offsets, block_r_ind, residue_r_ind,
+                              st_off, B, C, workspace, workspace_bytes, hot_columns, stream1, stream2);
 }
 
 }  // extern "C"

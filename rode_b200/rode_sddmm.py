@@ -112,18 +112,29 @@ def rode_sddmm(sparse_matrix: RoDeCSR, lhs: torch.Tensor, rhs: torch.Tensor) -> 
         lhs.contiguous(), rhs.contiguous(), k)
 
 
-def rode_spmm(sparse_matrix: RoDeCSR, dense: torch.Tensor) -> torch.Tensor:
+def rode_spmm(sparse_matrix: RoDeCSR, dense: torch.Tensor, hints: bool = True) -> torch.Tensor:
     """C = S @ dense for dense [n, width], width a multiple of 32.  Needs metadata from
-    seg_length 512 (k = 32 or 64 at construction); the reference has no Python SpMM."""
+    seg_length 512 (k = 32 or 64 at construction); the reference has no Python SpMM.
+
+    ``hints``: gather popular columns' rows with an L2 policy that keeps them resident
+    (same results, fewer DRAM bytes on skewed matrices).  The popularity bitmap is built on
+    the first call for a given width and cached on ``sparse_matrix``."""
     if sparse_matrix.CONFIGS[sparse_matrix.k]["k_block"] != 32:
         raise ValueError("SpMM needs k_block = 32 metadata")
     if dense.dim() != 2 or dense.shape[0] != sparse_matrix.n:
         raise ValueError(f"dense must be ({sparse_matrix.n}, width), got {tuple(dense.shape)}")
     assert dense.is_cuda and dense.device == sparse_matrix.device and dense.dtype == torch.float32
+    hot = None
+    if hints and dense.shape[1] % 128 == 0:
+        cache = sparse_matrix.__dict__.setdefault("_hot_columns", {})
+        row_bytes = dense.shape[1] * dense.element_size()
+        if row_bytes not in cache:
+            cache[row_bytes] = rode_sddmm_cuda.hot_columns(sparse_matrix.column_indices, sparse_matrix.n, row_bytes)
+        hot = cache[row_bytes]
     return rode_sddmm_cuda.spmm_forward(
         sparse_matrix.block_indices, sparse_matrix.residue_indices, sparse_matrix.st_offsets, sparse_matrix.m1,
         sparse_matrix.m2, sparse_matrix.row_offsets, sparse_matrix.column_indices, sparse_matrix.values,
-        sparse_matrix.m, sparse_matrix.n, dense.contiguous())
+        sparse_matrix.m, sparse_matrix.n, dense.contiguous(), hot)
 
 
 def torch_sddmm_reference(sparse_csr: torch.Tensor, lhs_matrix: torch.Tensor, rhs_matrix: torch.Tensor) -> torch.Tensor:

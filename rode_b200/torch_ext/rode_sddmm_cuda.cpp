@@ -15,7 +15,7 @@
 //     synchronising and destroying two streams per call
 //     (RoDe_SDDMM/rode_sddmm_cuda.cu:203-246); it does not block the host.
 //   * k_version may also be 64.
-//   * spmm_forward is new: the reference has no Python entry for SpMM.
+//   * spmm_forward and hot_columns are new: the reference has no Python entry for SpMM.
 #include <ATen/cuda/CUDAContext.h>
 #include <ATen/cuda/CUDAEvent.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -130,9 +130,34 @@ torch::Tensor py_sddmm_forward(torch::Tensor block_indices, torch::Tensor residu
     return out;
 }
 
+// Popularity bitmap of the columns for spmm_forward's `hot_columns` argument (rode_hot_columns),
+// or None when the library finds that marks would not help.  Reads the flag word back.
+c10::optional<torch::Tensor> py_hot_columns(torch::Tensor column_indices, int n_cols, int64_t dense_row_bytes,
+                                            int64_t budget_bytes) {
+    RODE_CHECK_INPUT(column_indices);
+    RODE_CHECK_INT(column_indices);
+    TORCH_CHECK(n_cols >= 0 && dense_row_bytes > 0 && budget_bytes >= 0, "bad size argument");
+    const c10::cuda::CUDAGuard guard(column_indices.device());
+    size_t words = 0, ws_bytes = 0;
+    check_status(rode_hot_columns_words(n_cols, &words));
+    check_status(rode_hot_columns_workspace_bytes(n_cols, &ws_bytes));
+    auto opts = column_indices.options();
+    torch::Tensor bitmap = torch::empty({static_cast<long long>(words)}, opts);
+    torch::Tensor ws = torch::empty({static_cast<long long>(ws_bytes)}, opts.dtype(torch::kUInt8));
+    auto stream = at::cuda::getCurrentCUDAStream(column_indices.device().index());
+    check_status(rode_hot_columns(column_indices.numel(), n_cols, column_indices.data_ptr<int>(),
+                                  static_cast<size_t>(dense_row_bytes), static_cast<size_t>(budget_bytes),
+                                  reinterpret_cast<unsigned *>(bitmap.data_ptr<int>()), ws.data_ptr(), ws_bytes,
+                                  stream.stream()));
+    const bool useful = bitmap[static_cast<long long>(words) - 1].item<int>() != 0;
+    if (!useful) return c10::nullopt;
+    return bitmap;
+}
+
 torch::Tensor py_spmm_forward(torch::Tensor block_indices, torch::Tensor residue_indices, torch::Tensor st_offsets,
                                 int m1, int m2, torch::Tensor row_offsets, torch::Tensor column_indices,
-                                torch::Tensor values, int m, int k, torch::Tensor dense) {
+                                torch::Tensor values, int m, int k, torch::Tensor dense,
+                                c10::optional<torch::Tensor> hot_columns) {
     RODE_CHECK_INPUT(block_indices);
     RODE_CHECK_INPUT(residue_indices);
     RODE_CHECK_INPUT(st_offsets);
@@ -159,18 +184,27 @@ torch::Tensor py_spmm_forward(torch::Tensor block_indices, torch::Tensor residue
     check_status(rode_spmm_workspace_bytes(m1, n, static_cast<int>(dense.element_size()), &ws_bytes));
     torch::Tensor ws = torch::empty({static_cast<long long>(std::max<size_t>(ws_bytes, 16))},
                                     dense.options().dtype(torch::kUInt8));
+    const unsigned *hot = nullptr;
+    if (hot_columns.has_value()) {
+        RODE_CHECK_INPUT(*hot_columns);
+        RODE_CHECK_INT(*hot_columns);
+        TORCH_CHECK(hot_columns->numel() == (static_cast<long long>(k) + 31) / 32 + 1,
+                    "hot_columns must come from hot_columns() for this matrix");
+        hot = reinterpret_cast<const unsigned *>(hot_columns->data_ptr<int>());
+    }
     fork_join(values.device(), [&](cudaStream_t s1, cudaStream_t s2) {
         if (dense.dtype() == torch::kFloat32)
-            check_status(rode_spmm_f32(m1, m2, k, n, values.data_ptr<float>(), column_indices.data_ptr<int>(),
-                                       row_offsets.data_ptr<int>(), block_indices.data_ptr<int>(),
-                                       residue_indices.data_ptr<int>(), st_offsets.data_ptr<int>(),
-                                       dense.data_ptr<float>(), out.data_ptr<float>(), ws.data_ptr(), ws_bytes, s1, s2));
+            check_status(rode_spmm_f32_hot(m1, m2, k, n, values.data_ptr<float>(), column_indices.data_ptr<int>(),
+                                           row_offsets.data_ptr<int>(), block_indices.data_ptr<int>(),
+                                           residue_indices.data_ptr<int>(), st_offsets.data_ptr<int>(),
+                                           dense.data_ptr<float>(), out.data_ptr<float>(), ws.data_ptr(), ws_bytes,
+                                           hot, s1, s2));
         else
-            check_status(rode_spmm_f64(m1, m2, k, n, values.data_ptr<double>(), column_indices.data_ptr<int>(),
-                                       row_offsets.data_ptr<int>(), block_indices.data_ptr<int>(),
-                                       residue_indices.data_ptr<int>(), st_offsets.data_ptr<int>(),
-                                       dense.data_ptr<double>(), out.data_ptr<double>(), ws.data_ptr(), ws_bytes, s1,
-                                       s2));
+            check_status(rode_spmm_f64_hot(m1, m2, k, n, values.data_ptr<double>(), column_indices.data_ptr<int>(),
+                                           row_offsets.data_ptr<int>(), block_indices.data_ptr<int>(),
+                                           residue_indices.data_ptr<int>(), st_offsets.data_ptr<int>(),
+                                           dense.data_ptr<double>(), out.data_ptr<double>(), ws.data_ptr(), ws_bytes,
+                                           hot, s1, s2));
     });
     // The workspace is used on the current stream only (block + fix-up kernels); the side
     // stream was joined back, so the caching allocator may reuse it after this call.
@@ -188,5 +222,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("rhs_matrix"), py::arg("k_version"));
     m.def("spmm_forward", &py_spmm_forward, "RoDe SpMM forward (CUDA)", py::arg("block_indices"),
           py::arg("residue_indices"), py::arg("st_offsets"), py::arg("m1"), py::arg("m2"), py::arg("row_offsets"),
-          py::arg("column_indices"), py::arg("values"), py::arg("m"), py::arg("k"), py::arg("dense"));
+          py::arg("column_indices"), py::arg("values"), py::arg("m"), py::arg("k"), py::arg("dense"),
+          py::arg("hot_columns") = py::none());
+    m.def("hot_columns", &py_hot_columns, "Column popularity bitmap for spmm_forward, or None (CUDA)",
+          py::arg("column_indices"), py::arg("n_cols"), py::arg("dense_row_bytes"), py::arg("budget_bytes") = 0);
 }

@@ -88,6 +88,27 @@ def test_rode_spmm_python_entry(api):
         assert torch.allclose(C.double(), want, rtol=1e-5, atol=1e-4 * max(1.0, (per_row / 16) ** 0.5))
 
 
+def test_rode_spmm_hints_cached_and_bit_identical(api):
+    """Width 128 on a skewed matrix: the popularity bitmap is built once, cached on the
+    matrix, and changes nothing in the result."""
+    from rode_b200 import workloads as W
+
+    dev = torch.device("cuda")
+    A = W.rmat(scale=18, device="cuda")
+    S = api.RoDeCSR(A.row_ptr.cpu(), A.col, A.val, dev, A.m, A.n, k=32)
+    X = torch.randn(A.n, 128, device=dev)
+    # the default budget (60 % of the L2) holds every touched row of this small matrix, so the
+    # library declines; a small explicit budget makes it mark columns
+    assert api.rode_sddmm_cuda.hot_columns(S.column_indices, S.n, 512) is None
+    hot = api.rode_sddmm_cuda.hot_columns(S.column_indices, S.n, 512, 4000 * 512)
+    assert hot is not None and hot.numel() == (A.n + 31) // 32 + 1
+    plain = api.rode_spmm(S, X, hints=False)
+    S.__dict__["_hot_columns"] = {512: hot}
+    hinted = api.rode_spmm(S, X)
+    assert torch.equal(plain, hinted)
+    assert S._hot_columns[512] is hot
+
+
 def test_launches_on_the_current_stream_without_blocking(api):
     dev = torch.device("cuda")
     S = api.RoDeCSR.from_random(2048, 2048, 64, dev, k=128)
