@@ -44,7 +44,7 @@ FALLBACK_HBM_GBS = 6650.0
 # (summarised in profiles/spmm_dram_traffic_rmat23_n128.md).
 NCU_TRAFFIC_BYTES = {23: 27331223808 + 286452992, 21: 3849421824 + 93184512}
 # the same capture with the column popularity hints in use (default budget)
-NCU_TRAFFIC_BYTES_HINTS = {23: 22339756032 + 286452992}
+NCU_TRAFFIC_BYTES_HINTS = {23: 22343146552 + 279467208}  # average of 23 launches, profiles/bench_launch_list_rmat23.md
 
 
 def parse_args():

@@ -72,30 +72,53 @@ degree_histogram(int n_cols, const int *__restrict__ degree, unsigned *__restric
     }
 }
 
-// One CTA.  Walks the bins from the highest in-degree down.
+// One CTA.  Walks the bins from the highest in-degree down: whole groups of kGroup bins
+// first (their sums come from one thread each), single bins inside the group where the
+// budget runs out.
+constexpr int kGroup = kBins / kThreads;  // bins per thread
 __global__ void __launch_bounds__(kThreads)
 pick_threshold(long long max_hot_columns, const unsigned *__restrict__ bin_columns,
                const unsigned *__restrict__ bin_references, HotState *__restrict__ state) {
     __shared__ unsigned s_cols[kBins];
     __shared__ unsigned s_refs[kBins];
-    for (int b = threadIdx.x; b < kBins; b += kThreads) {
+    __shared__ long long g_cols[kThreads];
+    __shared__ long long g_refs[kThreads];
+    long long my_cols = 0, my_refs = 0;
+    for (int i = 0; i < kGroup; ++i) {
+        const int b = threadIdx.x * kGroup + i;
         s_cols[b] = bin_columns[b];
         s_refs[b] = bin_references[b];
+        my_cols += s_cols[b];
+        my_refs += s_refs[b];
     }
+    g_cols[threadIdx.x] = my_cols;
+    g_refs[threadIdx.x] = my_refs;
     __syncthreads();
     if (threadIdx.x != 0) return;
-    long long touched = 0, references = 0;
-    for (int b = 1; b < kBins; ++b) {
-        touched += s_cols[b];
-        references += s_refs[b];
+    long long touched = 0, references = 0;  // bin 0 (columns without a reference) is never filled
+    for (int t = 0; t < kThreads; ++t) {
+        touched += g_cols[t];
+        references += g_refs[t];
     }
     long long hot = 0, hot_refs = 0;
     int threshold = kBins;  // nothing hot yet
-    for (int b = kBins - 1; b >= 2; --b) {
-        if (hot + s_cols[b] > max_hot_columns) break;
-        hot += s_cols[b];
-        hot_refs += s_refs[b];
-        threshold = b;
+    bool open = true;
+    for (int t = kThreads - 1; t >= 0 && open; --t) {
+        if (t > 0 && hot + g_cols[t] <= max_hot_columns) {  // the whole group fits
+            hot += g_cols[t];
+            hot_refs += g_refs[t];
+            threshold = t * kGroup;
+            continue;
+        }
+        for (int b = t * kGroup + kGroup - 1; b >= t * kGroup && b >= 2; --b) {
+            if (hot + s_cols[b] > max_hot_columns) {
+                open = false;
+                break;
+            }
+            hot += s_cols[b];
+            hot_refs += s_refs[b];
+            threshold = b;
+        }
     }
     // useful: the touched rows do not nearly fit the budget anyway, and the hot columns get
     // at least twice their share of the references
