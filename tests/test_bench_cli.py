@@ -30,6 +30,14 @@ def test_reference_arm_prints_one_json_line(oracle_cpu):
     assert d["config"]["workload"].endswith("spmm_n128") and d["steps"] == 2
 
 
+def test_reference_arm_uses_all_cores_under_a_launcher_that_sets_omp_threads(oracle_cpu):
+    """torchrun exports OMP_NUM_THREADS=1; the reference arm must still use the host's cores."""
+    res = _run("--impl", "reference", "--scale", "12", "--steps", "1", "--warmup", "1", env={"OMP_NUM_THREADS": "1"})
+    assert res.returncode == 0, res.stderr
+    d = json.loads(res.stdout.strip().splitlines()[-1])
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+
+
 def test_reference_arm_other_ranks_exit_silently():
     res = _run("--impl", "reference", "--gpus", "2", "--scale", "12", "--steps", "1", env={"RANK": "1", "WORLD_SIZE": "2"})
     assert res.returncode == 0 and res.stdout.strip() == ""
