@@ -15,6 +15,11 @@ SpMM -> D2H every step), `sddmm` (K = 64 on the same matrix), `cpu_baseline` (CP
 the host cores, N = 1 only) and, at N = 1, `configs`: the other benchmark matrices with the
 reference's own kernels (compiled for sm_100a into oracle/_ref) timed beside ours.
 
+`--hints on` (default) lets the SpMM use the library's column popularity hints where the
+library finds them useful (built once at set-up like the preprocessing, and again in every
+end-to-end step because the matrix arrives with the step); `--hints off` runs the plain
+entry point.  `hints` in the line says what was used and what the pass cost.
+
 `--impl reference` times the CPU implementation (the oracle's restatement of CSR SpMM; the
 reference has no CPU SpMM of its own) on all host threads and prints the same line shape.
 """
