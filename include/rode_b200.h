@@ -123,10 +123,13 @@ int rode_preprocess_cpu(int seg_len, int k_block, int vec_len, int M, const int 
  * 32 elements for float, 16 for double.  Block segments run on stream1, pure-residue rows
  * on stream2; the caller synchronises both, as with the reference.
  *
- * Differences a caller can observe: every row that appears in block_r_ind or
- * residue_r_ind is WRITTEN (not accumulated), without floating-point atomics, so results
- * are deterministic and C needs zero-filling only for the rows in neither list (empty rows
- * at an aligned offset), exactly the rows the reference never touches.
+ * Differences a caller can observe: every row with at least one nonzero is WRITTEN (not
+ * accumulated), without floating-point atomics, so results are deterministic.  Rows without
+ * a nonzero are never touched: C must be zero there, which the reference's contract (C
+ * zero-filled by the caller) already guarantees.  (The reference stores explicit zeros into
+ * the empty rows of its residue list, RoDeSpmm.cu:185-194; with a zero-filled C the result
+ * is the same, and on graphs with many empty rows those stores were half of the residue
+ * kernel's DRAM writes.)
  *
  * Rows split over several segments are summed through `workspace`
  * (rode_spmm_workspace_bytes(m1, n, sizeof(T)) bytes, 16-byte aligned, may be null when

@@ -32,8 +32,9 @@
 //    the same batched gather; a row is stored when the stream passes its end.
 //    spmm_rows_simple (L < 32): one lane group per residue row; spmm_rows_wide: one warp per
 //    row, for lists too short to fill the GPU.
-//    Empty rows in the list are stored as zeros, as the reference does
-//    (RoDeSpmm.cu:185-194); rows with a block part are skipped (spmm_block finished them).
+//    Rows of the list without a nonzero are not touched (the reference stores zeros there,
+//    RoDeSpmm.cu:185-194, into a C that its contract already wants zero-filled); rows with a
+//    block part are skipped (spmm_block finished them).
 //  * CTAs are one warp (four in spmm_rows_wide, whose rows are all shorter than 32): a CTA's
 //    slot is held until its slowest warp finishes, and segment lengths differ by more than 10x.
 //
@@ -307,16 +308,12 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
 
     // ---- descriptors: lane j of the group owns residue row item0 + j -----------------------
     int row = 0, begin = 0, len = 0;
-    bool listed = false;  // row is this kernel's to store
     if (l < rows_per_group && item0 + l < m2) {
         row = __ldg(residue_r_ind + item0 + l);
         begin = __ldg(row_offsets + row);
         const int end = __ldg(row_offsets + row + 1);
         // aligned length >= k_block: a block part exists and its last segment took the tail
-        if (end - begin + (begin % kAlign) < kBlockK) {
-            listed = true;
-            len = end - begin;
-        }
+        if (end - begin + (begin % kAlign) < kBlockK) len = end - begin;
     }
     int start = len;  // exclusive prefix sum of len inside the group
 #pragma unroll
@@ -332,14 +329,9 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
     const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
     V *c_lane = reinterpret_cast<V *>(C) + col_vec;
 
-    // ---- empty rows of the list: zeros ----------------------------------------------------------
-    unsigned zeros = (__ballot_sync(gmask, listed && len == 0) & gmask) >> gshift;
-    while (zeros) {
-        const int j = __ffs(zeros) - 1;
-        zeros &= zeros - 1;
-        const int r = __shfl_sync(gmask, row, j, L);
-        st_stream(c_lane + static_cast<size_t>(r) * row_vecs, vzero(static_cast<V *>(nullptr)));
-    }
+    // Rows of the list without a nonzero are left alone: C arrives zero-filled (the contract of
+    // the reference's entry points), and on graphs with many empty rows the zero rows were half
+    // of this kernel's DRAM writes.
     unsigned todo = (__ballot_sync(gmask, len > 0) & gmask) >> gshift;  // rows with nonzeros, in order
     if (todo == 0) return;
 
@@ -450,8 +442,9 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
     const int row = __ldg(residue_r_ind + item);
     const int begin = __ldg(row_offsets + row);
     const int end = __ldg(row_offsets + row + 1);
-    // aligned length >= k_block: a block part exists and its last segment took the tail
-    if (end - begin + (begin % kAlign) >= kBlockK) return;
+    // aligned length >= k_block: a block part exists and its last segment took the tail;
+    // no nonzero: the row stays as the caller zero-filled it
+    if (end - begin + (begin % kAlign) >= kBlockK || end == begin) return;
 
     const size_t row_vecs = static_cast<size_t>(n) / kLen;
     const size_t col_vec = static_cast<size_t>(blockIdx.y) * L * VPL + l;
@@ -536,6 +529,7 @@ spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restric
     const int end = __ldg(row_offsets + row + 1);
     if (end - begin + (begin % kAlign) >= kBlockK) return;  // the block part took this row's tail
     const int len = end - begin;                            // < 32
+    if (len == 0) return;                                   // stays as the caller zero-filled it
 
     int c = 0;
     T val = T(0);

@@ -84,10 +84,11 @@ def test_spmm_edge_cases(oracle_cpu):
             assert meta.m2 == 0 and meta.m1 > 0
         for n in (32, 128):
             B = W.dense(A.n, n, seed=6)
-            # rows named by the metadata are written, not accumulated: start from garbage there
+            # rows with a nonzero are written, not accumulated: start from garbage there; rows
+            # without one are never touched and stay as the caller zero-filled them
             C0 = torch.zeros((A.m, n), device="cuda")
-            listed = torch.cat([meta.block_r_ind[: meta.m1], meta.residue_r_ind[: meta.m2]]).long()
-            C0[listed] = float("nan")
+            nonempty = (d.row_ptr[1:] > d.row_ptr[:-1])
+            C0[nonempty] = float("nan")
             C = capi.spmm(meta, d.row_ptr, d.col, d.val, B.cuda(), C=C0)
             _check_against_truth(oracle_cpu, A, B.numpy(), C, f"{name} n={n}")
     # M == 0: nothing to launch
