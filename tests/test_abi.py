@@ -77,6 +77,28 @@ def test_argument_errors_are_reported_not_raised_by_cuda(built_library):
     assert lib.rode_sddmm_f32(0, 0, 8, 32, None, None, None, None, None, None, None, None, None, None, None) == 0
 
 
+def test_hot_columns_sizes_and_argument_errors(built_library):
+    """Host arithmetic and argument checks of the popularity-hint entry points (no device)."""
+    lib = capi.load()
+    words, need = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    assert lib.rode_hot_columns_words(0, ctypes.byref(words)) == 0 and words.value == 1
+    assert lib.rode_hot_columns_words(32, ctypes.byref(words)) == 0 and words.value == 2
+    assert lib.rode_hot_columns_words(33, ctypes.byref(words)) == 0 and words.value == 3
+    assert lib.rode_hot_columns_workspace_bytes(1000, ctypes.byref(need)) == 0
+    assert need.value >= 4 * 1000 + 2 * 4096 * 4 and need.value % 256 == 0
+    assert lib.rode_hot_columns_words(-1, ctypes.byref(words)) == capi.RODE_ERR_INVALID_ARGUMENT
+    # row bytes 0, null bitmap, missing / short / misaligned workspace
+    assert lib.rode_hot_columns(10, 64, 256, 0, 0, 256, 256, 1 << 20, None) == capi.RODE_ERR_INVALID_ARGUMENT
+    assert lib.rode_hot_columns(10, 64, 256, 512, 0, None, 256, 1 << 20, None) == capi.RODE_ERR_INVALID_ARGUMENT
+    assert lib.rode_hot_columns(10, 64, 256, 512, 0, 256, None, 0, None) == capi.RODE_ERR_WORKSPACE
+    assert lib.rode_hot_columns(10, 64, 256, 512, 0, 256, 256, 16, None) == capi.RODE_ERR_WORKSPACE
+    assert lib.rode_hot_columns(10, 64, 256, 512, 1, 256, 264, 1 << 20, None) == capi.RODE_ERR_WORKSPACE
+    assert b"aligned" in lib.rode_last_error()
+    # the hinted SpMM entry points validate like the plain ones
+    assert lib.rode_spmm_f32_hot(1, 1, 8, 20, 16, 16, 16, 16, 16, 16, 16, 16, None, 0, 16, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
+    assert lib.rode_spmm_f64_hot(0, 0, 8, 32, None, None, None, None, None, None, None, None, None, 0, None, None, None) == 0
+
+
 def test_host_preprocess_twin_matches_oracle_and_fixtures(built_library, oracle_cpu, golden_dir):
     g = np.load(os.path.join(golden_dir, "preprocess_golden.npz"))
     for case in sorted({k.split("/")[0] for k in g.files}):
