@@ -685,7 +685,9 @@ def main():
                                   if ms_block else None),
                      "note": "rank 0's launch; bytes requested from L1/L2/HBM, of which `traffic` reach DRAM"},
         "step": {"algorithmic_bytes": step_bytes_all, "achieved": step_bytes_all / ms_step / 1e6,
-                 "frac": step_bytes_all / ms_step / 1e6 / (peak_gbs * world)},
+                 "frac": step_bytes_all / ms_step / 1e6 / (peak_gbs * world),
+                 "note": "B_min = 8*nnz + 4*(M+1) + 4*N*K_touched + 4*N*M counts a C row for every row of the "
+                         "matrix; the kernels store only the rows that have a nonzero"},
     }
     traffic_table = NCU_TRAFFIC_BYTES_HINTS if hot is not None else NCU_TRAFFIC_BYTES
     if world == 1 and args.scale in traffic_table and not args.hint_budget_mb:
