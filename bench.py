@@ -43,13 +43,40 @@ N_DENSE = 128
 K_SDDMM = 64
 METRIC = "SpMM GFLOP/s (2*nnz*N), fp32"
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes of ONE rode::spmm_block launch of the headline workload, keyed by R-MAT scale,
-# from a single-pass ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of
-# `python bench.py --only spmm --family rmat --scale S --width 128 --steps 1 --warmup 1`
-# (summarised in profiles/spmm_dram_traffic_rmat23_n128.md).
-NCU_TRAFFIC_BYTES = {23: 27331223808 + 286452992, 21: 3849421824 + 93184512}
-# the same capture with the column popularity hints in use (default budget)
-NCU_TRAFFIC_BYTES_HINTS = {23: 22343146552 + 279467208}  # average of 23 launches, profiles/bench_launch_list_rmat23.md
+# Measured DRAM traffic of one rode::spmm_block launch (ncu, single-pass capture of the two DRAM
+# byte counters).  The file records which build of the SpMM sources the capture saw; when the
+# sources have changed since, the number no longer describes the kernel that is timed here and
+# `traffic` is reported as null.
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "spmm_block_dram_traffic.json")
+KERNEL_SOURCES = ("rode_b200/csrc/rode_spmm.cu", "rode_b200/csrc/rode_common.cuh")
+
+
+def kernel_source_digest() -> str:
+    import hashlib
+
+    h = hashlib.sha256()
+    for rel in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, rel), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def measured_traffic(scale: int, hints: bool):
+    """(bytes per launch, description) from the capture record, or (None, why not)."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            rec = json.load(f)
+    except Exception:
+        return None, "no capture record"
+    if rec.get("kernel_source_digest") != kernel_source_digest():
+        return None, "the SpMM sources changed after the last ncu capture; no DRAM byte count for this build"
+    key = f"rmat{scale}_n{N_DENSE}_{'hints' if hints else 'plain'}"
+    entry = rec.get("captures", {}).get(key)
+    if entry is None:
+        return None, f"no capture of {key}"
+    return int(entry["dram_bytes_per_launch"]), (f"ncu dram__bytes_read.sum + dram__bytes_write.sum of "
+                                                 f"{entry['kernel']}, {entry['launches']} launch(es), "
+                                                 f"captured at commit {rec.get('commit', '?')}")
 
 
 def parse_args():
@@ -60,7 +87,12 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--scale", type=int, default=23, help="R-MAT scale of the headline workload")
     p.add_argument("--no-extra", action="store_true", help="skip the secondary configs and the CPU baseline")
-    p.add_argument("--e2e-steps", type=int, default=6)
+    p.add_argument("--e2e-steps", type=int, default=10)
+    p.add_argument("--repeats", type=int, default=0,
+                   help="timed repeats of the --steps loop (0 = at least 10 and at least one second of device time)")
+    p.add_argument("--e2e-row-weight", type=float, default=64.0,
+                   help="multi-GPU partition of the end-to-end run: cost of a row = its nnz + this; 64 balances the "
+                        "bytes a rank moves over PCIe (8 B per nonzero in, 4*N = 512 B per row out)")
     p.add_argument("--row-weight", type=float, default=2.0,
                    help="multi-GPU partition: cost of a row = its nnz + this (0 = plain nnz-balanced)")
     p.add_argument("--hints", choices=["on", "off"], default="on",
@@ -186,7 +218,7 @@ def time_loop(fn, steps, warmup, stream, flush=None):
     return statistics.median(times)
 
 
-def time_preprocess(row_ptr, nnz, seg, iters, peak_gbs, with_host=True):
+def time_preprocess(row_ptr, nnz, seg, iters, peak_gbs, with_host=True, with_swizzle=True):
     """Device time of the three preprocessing kernels (raw entry point, buffers allocated
     once), the host twin's single-thread time, and the HBM roofline of the device version:
     algorithmic bytes = row pointer read once + outputs written once."""
@@ -212,6 +244,13 @@ def time_preprocess(row_ptr, nnz, seg, iters, peak_gbs, with_host=True):
     algo = 4 * (M + 1) + 8 * m1 + 4 + 4 * m2 + 8
     out = {"seg_len": seg, "rows": M, "m1": m1, "m2": m2, "gpu_ms": ms, "algorithmic_bytes": algo,
            "algorithmic_gbs": algo / ms / 1e6, "frac_of_measured_hbm": algo / ms / 1e6 / peak_gbs}
+    if with_swizzle:
+        # the comparator the reference times beside its own preprocessing: rows sorted by
+        # decreasing length (Preprocess_opt/_preprocess.cu:71-104, a thrust sort_by_key there)
+        from rode_b200 import matrix_io
+
+        out["swizzle_gpu_ms"] = time_loop(lambda: matrix_io.row_swizzle(row_ptr), min(iters, 10), 2, stream)
+        out["swizzle_over_rode"] = out["swizzle_gpu_ms"] / ms
     if with_host:
         rp_host = row_ptr.cpu()
         t0 = time.perf_counter()
@@ -267,36 +306,55 @@ class ForkJoin:
 
 
 # ---------------------------------------------------------------------------------------
+def headline_matrix(scale: int, device):
+    from rode_b200 import workloads as W
+
+    return W.rmat(scale=scale, device=device)
+
+
 def reference_arm(args, rank, world):
     """CPU implementation on the host cores: the oracle's CSR SpMM (the reference ships no
-    CPU SpMM), all threads, on a bounded sample of the headline workload."""
+    CPU SpMM), all threads, whole passes over the SAME matrix and dense operand as the GPU arm
+    (same generator, seed, scale and width); `--steps` timed passes after `--warmup` untimed
+    ones.  Only rank 0 works; the other ranks of a multi-process launch leave at once."""
     if rank != 0:
         return None
     from oracle import cpu
     from rode_b200 import workloads as W
 
     threads = cpu.max_threads()
-    scale = min(args.scale, 20)  # bounded sample: same generator and width, 2^20 vertices
-    A = W.rmat(scale=scale, device="cpu")
-    B = W.dense(A.n, N_DENSE, seed=3).numpy()
-    rp, col, val = A.row_ptr.numpy(), A.col.numpy(), A.val.numpy()
-    warm = max(1, min(args.warmup, 3))
+    # the generator draws the same matrix on either device type only from the same kind of
+    # random stream, so it runs where the GPU arm runs it (on the GPU when one is visible)
+    gen_dev = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    A = headline_matrix(args.scale, gen_dev)
+    B = W.dense(A.n, N_DENSE, device=gen_dev, seed=3).cpu().numpy()
+    rp, col, val = A.row_ptr.cpu().numpy(), A.col.cpu().numpy(), A.val.cpu().numpy()
+    m, n_cols, nnz = A.m, A.n, A.nnz
+    del A
+    if gen_dev.type == "cuda":
+        torch.cuda.empty_cache()
+    warm = max(0, args.warmup)
     for _ in range(warm):
         cpu.spmm_f32(rp, col, val, B, threads=threads)
     steps = max(1, args.steps)
-    t0 = time.perf_counter()
+    times = []
     for _ in range(steps):
-        cpu.spmm_f32(rp, col, val, B, threads=threads)
-    ms = (time.perf_counter() - t0) / steps * 1e3
-    gflops = 2.0 * A.nnz * N_DENSE / (ms * 1e-3) / 1e9
-    sample = f"R-MAT scale {scale} (nnz {A.nnz}), N={N_DENSE}, full pass per step"
+        t0 = time.perf_counter()
+        out = cpu.spmm_f32(rp, col, val, B, threads=threads)
+        times.append((time.perf_counter() - t0) * 1e3)
+    ms = sum(times) / steps
+    gflops = 2.0 * nnz * N_DENSE / (ms * 1e-3) / 1e9
+    sample = (f"whole passes over the headline matrix (R-MAT scale {args.scale}, nnz {nnz}, N={N_DENSE}), "
+              f"{ms / 1e3:.3f} s per pass, matrix drawn on {gen_dev.type}")
     line = {
         "impl": "reference", "metric": METRIC, "value": gflops, "unit": "GFLOP/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "steps": steps, "warmup": warm, "ms_per_step": ms, "ms_per_step_median": statistics.median(times),
+        "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"rmat{args.scale}_spmm_n{N_DENSE}", "sample": sample},
+        "config": {"workload": f"rmat{args.scale}_spmm_n{N_DENSE}", "rows": m, "nnz": nnz, "n": N_DENSE},
         "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gflops, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "checksum": float(out.astype("float64").sum()),
     }
     return line
 
@@ -332,6 +390,7 @@ def secondary_configs(peak_gbs, steps, warmup):
             entry = {"nnz": A.nnz, "m1": meta.m1, "m2": meta.m2}
             pre = time_preprocess(A.row_ptr, A.nnz, seg, 10, peak_gbs, with_host=False)
             entry["preprocess_gpu_ms"] = pre["gpu_ms"]
+            entry["swizzle_gpu_ms"] = pre["swizzle_gpu_ms"]
             if op in ("spmm", "spmm_f64"):
                 dt = torch.float64 if op == "spmm_f64" else torch.float32
                 esz = 8 if op == "spmm_f64" else 4
@@ -454,7 +513,7 @@ def make_family(name, device, scale=23, size=1.0):
 
 def single_op(args):
     """One family, one op, one width on cuda:0: `warmup` untimed and `steps` timed launches of
-    the entry point and nothing else (the run the ncu summaries under profiles/ come from)."""
+    the entry point and nothing else (a run small enough to profile)."""
     from rode_b200 import capi
     from rode_b200 import workloads as W
 
@@ -575,7 +634,7 @@ def main():
     t_setup = time.perf_counter()
     n_vert = 1 << args.scale
     if rank == 0:
-        A = W.rmat(scale=args.scale, device=dev)
+        A = headline_matrix(args.scale, dev)
         sizes = torch.tensor([A.nnz], dtype=torch.int64, device=dev)
     else:
         A = None
@@ -608,6 +667,14 @@ def main():
     bounds = W.partition_rows(row_ptr, world, args.row_weight)
     r0, r1 = bounds[rank], bounds[rank + 1]
     mine = full.rows(r0, r1)
+    # The end-to-end run is bound by PCIe, not by the kernels, so its rows are cut by the bytes
+    # a rank moves per step (8 B per nonzero in, 4*N B per row of C out) instead of by kernel cost.
+    if world > 1 and args.e2e_row_weight != args.row_weight:
+        e2e_bounds = W.partition_rows(row_ptr, world, args.e2e_row_weight)
+        e2e_r0, e2e_r1 = e2e_bounds[rank], e2e_bounds[rank + 1]
+        mine_e2e = full.rows(e2e_r0, e2e_r1)
+    else:
+        e2e_r0, e2e_r1, mine_e2e = r0, r1, mine
     if world > 1:
         del full, row_ptr, col, val
         torch.cuda.empty_cache()
@@ -637,22 +704,41 @@ def main():
         fj.run(spmm_launch)
 
     # ---- timed region -------------------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
+    # EXACTLY `steps` steps between a barrier + synchronize on both sides, timed with CUDA
+    # events on the launching stream, max over ranks; the whole bracket is repeated and the
+    # median repeat reported, so that the timed region spans at least a second and one slow
+    # repeat (clock ramp, power cap) does not decide the number.
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step()
     barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed_repeat():
+        barrier()
+        a.record(fj.cur)
+        for _ in range(args.steps):
+            step()
+        b.record(fj.cur)
+        barrier()
+        return max_over_ranks(a.elapsed_time(b) / args.steps)
+
+    first = timed_repeat()                      # also sizes the number of repeats
+    repeats = args.repeats if args.repeats > 0 else max(10, int(1000.0 / max(first * args.steps, 1e-3)) + 1)
+    repeats = min(repeats, 200)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record(fj.cur)
-    for _ in range(args.steps):
-        step()
-    b.record(fj.cur)
-    barrier()
+    repeat_ms = [timed_repeat() for _ in range(repeats)]
     clocks = sampler.stop() if rank == 0 else None
-    ms_step = max_over_ranks(a.elapsed_time(b) / args.steps)
+    ms_step = statistics.median(repeat_ms)
     launches_per_step = (2 if meta.m1 > 0 else 0) + (1 if meta.m2 > 0 else 0)
     gflops = 2.0 * nnz * N_DENSE / ms_step / 1e6
+    timing = {"repeats": repeats, "steps_per_repeat": args.steps, "ms_per_step_of_each_repeat": repeat_ms,
+              "ms_per_step_min": min(repeat_ms), "ms_per_step_max": max(repeat_ms),
+              "timed_region_s": sum(repeat_ms) * args.steps / 1e3,
+              # time x clock: comparable between boxes whose power cap settles at different clocks
+              "ms_per_step_x_sm_mhz": (ms_step * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None}
 
     # ---- per-kernel timing and the roofline of the dominant kernel ---------------------------
     lens = (mine.row_ptr[1:] - mine.row_ptr[:-1]).to(torch.int64)
@@ -689,12 +775,33 @@ def main():
                  "note": "B_min = 8*nnz + 4*(M+1) + 4*N*K_touched + 4*N*M counts a C row for every row of the "
                          "matrix; the kernels store only the rows that have a nonzero"},
     }
-    traffic_table = NCU_TRAFFIC_BYTES_HINTS if hot is not None else NCU_TRAFFIC_BYTES
-    if world == 1 and args.scale in traffic_table and not args.hint_budget_mb:
-        roofline["traffic"] = traffic_table[args.scale]
-        roofline["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one spmm_block launch on "
-                                      "this workload" + (", popularity hints in use" if hot is not None else ""))
-        roofline["traffic_gbs"] = traffic_table[args.scale] / ms_block / 1e6 if ms_block else None
+    if world == 1 and not args.hint_budget_mb:
+        traffic, source = measured_traffic(args.scale, hot is not None)
+        roofline["traffic"] = traffic
+        roofline["traffic_source"] = source
+        roofline["traffic_gbs"] = traffic / ms_block / 1e6 if traffic and ms_block else None
+    # What this access order can reach at best with an ideal cache of the L2's size: the C most
+    # referenced dense rows (C = L2 bytes / row bytes) are fetched once and then always hit, every
+    # other reference misses.  A lower bound of the block kernel's DRAM bytes that, unlike B_min,
+    # knows that the gathers of a row-major pass cannot all be served from a 126 MB cache.
+    if meta.m1 > 0:
+        l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
+        cached = l2_bytes // (4 * N_DENSE)
+        deg = torch.bincount(mine.col[torch.repeat_interleave(in_block, lens)].long(), minlength=1)
+        deg_sorted, _ = torch.sort(deg[deg > 0], descending=True)
+        refs_total = int(deg_sorted.sum())
+        refs_cached = int(deg_sorted[:cached].sum())
+        cols_cached = int(min(cached, deg_sorted.numel()))
+        floor_bytes = (8 * nnz_block + 4 * N_DENSE * (cols_cached + refs_total - refs_cached)
+                       + 4 * N_DENSE * rows_block)
+        roofline["floor_model"] = {
+            "bytes_per_launch": floor_bytes, "cache_bytes": l2_bytes, "cached_columns": cols_cached,
+            "references_served_from_cache": refs_cached / max(refs_total, 1),
+            "ms_at_peak": floor_bytes / peak_gbs / 1e6,
+            "frac": (floor_bytes / ms_block / 1e6 / peak_gbs) if ms_block else None,
+            "note": "ideal-cache lower bound of DRAM bytes for a row-major pass: the most referenced dense rows "
+                    "that fit the whole L2 are read once, every other gather misses; rank 0's launch"}
+        del deg, deg_sorted
 
     # ---- SDDMM K = 64 on the same rows ---------------------------------------------------------
     lhs = W.dense(n_vert, K_SDDMM, device=dev, seed=5)[r0:r1].contiguous()
@@ -718,12 +825,21 @@ def main():
     # Host side of the job: every rank holds its CSR slice and, at N > 1, 1/N of the dense
     # operand's rows in pinned memory; the operand is assembled on the GPUs by one all-gather
     # over NVLink per step instead of N full copies over PCIe.
-    h_rp, h_col, h_val = (t.cpu().pin_memory() for t in (mine.row_ptr, mine.col, mine.val))
+    del C
+    src = mine_e2e
+    e_nnz, e_rows = src.nnz, src.m
+    h_rp, h_col, h_val = (t.cpu().pin_memory() for t in (src.row_ptr, src.col, src.val))
     shard = n_vert // world
     h_X = X[rank * shard:(rank + 1) * shard].cpu().pin_memory() if world > 1 else X.cpu().pin_memory()
-    h_C = torch.empty((my_rows, N_DENSE), dtype=torch.float32).pin_memory()
+    h_C = torch.empty((e_rows, N_DENSE), dtype=torch.float32).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in (h_rp, h_col, h_val, h_X))
     d2h = h_C.numel() * 4
+    # workspace for the split rows of the end-to-end slice (an application knows its matrix: sized once)
+    if src is mine:
+        ws_e, ws_e_bytes = ws, ws_bytes
+    else:
+        ws_e_bytes = capi.spmm_workspace_bytes(capi.preprocess(src.row_ptr, e_nnz, 512, 32, 4).m1, N_DENSE, 4)
+        ws_e = torch.empty(max(ws_e_bytes, 16), dtype=torch.uint8, device=dev)
     # Software pipeline over steps: two sets of device input buffers and two result buffers,
     # one copy-in stream, the compute streams, one copy-out stream.  Step i+1's H2D runs while
     # step i computes and step i's result goes back (PCIe is full duplex).
@@ -731,14 +847,13 @@ def main():
     bufs = []
     for _ in range(2):
         bufs.append({
-            "rp": torch.empty_like(mine.row_ptr), "col": torch.empty_like(mine.col), "val": torch.empty_like(mine.val),
+            "rp": torch.empty_like(src.row_ptr), "col": torch.empty_like(src.col), "val": torch.empty_like(src.val),
             "X": (torch.empty((shard, N_DENSE), dtype=torch.float32, device=dev) if world > 1 else torch.empty_like(X)),
-            "C": torch.empty((my_rows, N_DENSE), dtype=torch.float32, device=dev),
+            "C": torch.empty((e_rows, N_DENSE), dtype=torch.float32, device=dev),
             "in_ready": torch.cuda.Event(), "in_free": torch.cuda.Event(), "out_ready": torch.cuda.Event(),
             "out_free": torch.cuda.Event(),
         })
     d_X_full = torch.empty_like(X) if world > 1 else None
-    del C
 
     def copy_in(i):
         bf = bufs[i % 2]
@@ -757,7 +872,7 @@ def main():
         if world > 1:
             dist.all_gather_into_tensor(d_X_full, bf["X"])
         dense_x = d_X_full if world > 1 else bf["X"]
-        m = capi.preprocess(bf["rp"], my_nnz, 512, 32, 4)   # device-side row decomposition (reads 2 counts back)
+        m = capi.preprocess(bf["rp"], e_nnz, 512, 32, 4)    # device-side row decomposition (reads 2 counts back)
         # the matrix arrived with this step, so its popularity bitmap is built in this step too
         h = (capi.hot_columns(bf["col"], n_vert, 4 * N_DENSE, budget_bytes=int(args.hint_budget_mb * 1e6))
              if args.hints == "on" else None)
@@ -766,8 +881,8 @@ def main():
         def launch(s1, s2):
             capi.spmm_raw(torch.float32, m.m1, m.m2, n_vert, N_DENSE, bf["val"].data_ptr(), bf["col"].data_ptr(),
                           bf["rp"].data_ptr(), m.block_r_ind.data_ptr(), m.residue_r_ind.data_ptr(),
-                          m.st_off.data_ptr(), dense_x.data_ptr(), bf["C"].data_ptr(), ws.data_ptr(), ws_bytes, s1, s2,
-                          hot=None if h is None else h.data_ptr())
+                          m.st_off.data_ptr(), dense_x.data_ptr(), bf["C"].data_ptr(), ws_e.data_ptr(), ws_e_bytes,
+                          s1, s2, hot=None if h is None else h.data_ptr())
 
         fj.run(launch)
         bf["in_free"].record(fj.cur)
@@ -786,20 +901,59 @@ def main():
         fj.cur.wait_event(bufs[(steps - 1) % 2]["out_free"])   # the last result is on the host
 
     e2e_run(1)
+    # each direction alone, all ranks at once (what the host's PCIe and memory give N concurrent copies)
+    def alone(fn):
+        barrier()
+        a.record(fj.cur)
+        with torch.cuda.stream(fj.cur):
+            fn()
+        b.record(fj.cur)
+        barrier()
+        return a.elapsed_time(b)
+
+    def all_inputs():
+        for name, h in (("rp", h_rp), ("col", h_col), ("val", h_val), ("X", h_X)):
+            bufs[0][name].copy_(h, non_blocking=True)
+
+    ms_h2d_alone = alone(all_inputs)
+    ms_d2h_alone = alone(lambda: h_C.copy_(bufs[0]["C"], non_blocking=True))
     barrier()
     a.record(fj.cur)
     e2e_run(args.e2e_steps)
     b.record(fj.cur)
     barrier()
-    ms_e2e = max_over_ranks(a.elapsed_time(b) / args.e2e_steps)
+    ms_e2e_mine = a.elapsed_time(b) / args.e2e_steps
+    ms_e2e = max_over_ranks(ms_e2e_mine)
+    # every rank's share, gathered on all ranks (rank 0 prints it)
+    mine_row = torch.tensor([e_rows, e_nnz, h2d, d2h, ms_e2e_mine, ms_h2d_alone, ms_d2h_alone], dtype=torch.float64,
+                            device=dev)
+    if world > 1:
+        table = [torch.empty_like(mine_row) for _ in range(world)]
+        dist.all_gather(table, mine_row)
+    else:
+        table = [mine_row]
+    per_rank = [{"rank": i, "rows": int(t[0]), "nnz": int(t[1]), "h2d_bytes": int(t[2]), "d2h_bytes": int(t[3]),
+                 "ms_per_step": float(t[4]), "h2d_alone_ms": float(t[5]), "h2d_alone_gbs": float(t[2] / t[5] / 1e6),
+                 "d2h_alone_ms": float(t[6]), "d2h_alone_gbs": float(t[3] / t[6] / 1e6) if float(t[6]) > 0 else None}
+                for i, t in enumerate(table)]
+    slowest = max(per_rank, key=lambda r: r["ms_per_step"])
     e2e = {"value": 2.0 * nnz * N_DENSE / ms_e2e / 1e6, "unit": "GFLOP/s", "ms_per_step": ms_e2e,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
+           "h2d_bytes_per_step": int(sum(r["h2d_bytes"] for r in per_rank)),
+           "d2h_bytes_per_step": int(sum(r["d2h_bytes"] for r in per_rank)),
+           "bytes_are": "sums over all ranks; per_rank has each rank's share",
+           "steps": args.e2e_steps, "per_rank": per_rank,
+           "slowest_rank": {"rank": slowest["rank"],
+                            "bound_by": ("h2d" if slowest["h2d_alone_ms"] >= slowest["d2h_alone_ms"] else "d2h"),
+                            "note": "the longer of the rank's two copy directions, each timed alone with all ranks "
+                                    "copying at once; a pipelined step cannot be shorter than that"},
+           "partition": (f"contiguous rows, cost nnz + {args.e2e_row_weight}*rows (balances PCIe bytes per rank)"
+                         if world > 1 else "one rank"),
            "includes": ("every step: H2D of the rank's CSR slice + dense operand from pinned memory, device "
-                        "preprocessing, C zero-fill, SpMM, D2H of the rank's C rows; steps are software-pipelined "
-                        "(step i+1's H2D overlaps step i's compute and D2H)" if world == 1 else
+                        "preprocessing, popularity pass, C zero-fill, SpMM, D2H of the rank's C rows; steps are "
+                        "software-pipelined (step i+1's H2D overlaps step i's compute and D2H)" if world == 1 else
                         "every step, per rank: H2D of its CSR slice + 1/N of the dense operand from pinned memory, "
-                        "NCCL all-gather of the operand, device preprocessing, C zero-fill, SpMM, D2H of its C rows; "
-                        "steps are software-pipelined; bytes are rank 0's")}
+                        "NCCL all-gather of the operand, device preprocessing, popularity pass, C zero-fill, SpMM, "
+                        "D2H of its C rows; steps are software-pipelined")}
     checksum = float(h_C.double().sum())
 
     # ---- CPU baseline (rank 0, single-GPU run only) ----------------------------------------------
@@ -817,13 +971,13 @@ def main():
             passes += 1
         dt = (time.perf_counter() - t0) / passes
         # one thread (how the reference's own CPU code runs): the first 2^18 rows, one pass
-        rows_1 = min(my_rows, 1 << 18)
+        rows_1 = min(e_rows, 1 << 18)
         nnz_1 = int(rp_h[rows_1])
         t1 = time.perf_counter()
         cpu.spmm_f32(rp_h[: rows_1 + 1], col_h[:nnz_1], val_h[:nnz_1], X_h, threads=1)
         dt1 = time.perf_counter() - t1
-        cpu_baseline = {"value": 2.0 * my_nnz * N_DENSE / dt / 1e9, "unit": "GFLOP/s", "cores": threads, "kind": "port",
-                        "sample": f"{passes} full passes over the headline matrix (nnz {my_nnz}), {dt:.3f} s per pass",
+        cpu_baseline = {"value": 2.0 * e_nnz * N_DENSE / dt / 1e9, "unit": "GFLOP/s", "cores": threads, "kind": "port",
+                        "sample": f"{passes} full passes over the headline matrix (nnz {e_nnz}), {dt:.3f} s per pass",
                         "single_thread_value": 2.0 * nnz_1 * N_DENSE / dt1 / 1e9,
                         "single_thread_sample": f"rows 0..{rows_1} (nnz {nnz_1}), one pass, {dt1:.2f} s",
                         "note": "the reference has no CPU SpMM; this is the oracle's CSR SpMM with OpenMP over rows"}
@@ -834,7 +988,7 @@ def main():
     if rank == 0:
         line = {
             "metric": METRIC, "value": gflops, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"rmat{args.scale}_spmm_n{N_DENSE}", "rows": n_vert, "nnz": nnz, "n": N_DENSE,
                        "partition": (f"nnz-balanced contiguous rows over {world} rank(s)" if not args.row_weight else
@@ -842,7 +996,9 @@ def main():
                        "rank0_rows": my_rows, "rank0_nnz": my_nnz,
                        "l2": "inputs larger than L2 (dense operand 4.3 GB, CSR 1 GB); no flush between steps",
                        "m1_rank0": meta.m1, "m2_rank0": meta.m2},
-            "clocks": clocks, "gpu_launches": launches_per_step * args.steps, "nnz_per_s": nnz / ms_step * 1e3,
+            "clocks": clocks, "timing": timing,
+            "gpu_launches": launches_per_step * args.steps, "gpu_launches_note": "per repeat of the timed loop",
+            "nnz_per_s": nnz / ms_step * 1e3,
             "roofline": roofline, "e2e": e2e, "sddmm": sddmm, "preprocess": preprocess_info, "hints": hints_info,
             "cpu_baseline": cpu_baseline,
             "broadcast_ms": broadcast_ms, "setup_s": setup_s, "checksum": checksum,

@@ -14,10 +14,12 @@
  * reference's tiles do.  Failures (bad arguments, launch errors) cannot be returned through
  * a void function: they are recorded and can be read with rode_last_error().
  *
- * Rows cut into several segments are summed through a per-device workspace that the
- * library allocates on first use and re-uses; calls that overlap in time on one device
- * must therefore not both contain split rows (use rode_spmm_f32 with an explicit
- * workspace for that).
+ * Rows cut into several segments are summed through a workspace that the library keeps for
+ * these entry points: one growable device buffer per (device, stream1), allocated on the
+ * first call on that stream (cudaMalloc) and re-used afterwards.  Calls on the same stream1
+ * are ordered by the stream and share the buffer; calls on different streams get buffers of
+ * their own and may overlap on the GPU, as with the reference.  Callers that must not
+ * allocate at call time pass their own workspace to rode_spmm_f32 / rode_spmm_f64.
  */
 #ifndef RODE_B200_RODESPMM_H_
 #define RODE_B200_RODESPMM_H_

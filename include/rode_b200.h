@@ -99,7 +99,9 @@ int rode_preprocess(int seg_len, int k_block, int vec_len, int M, const int *row
  *   Set-up    the first call on each device looks up the array's device address (the
  *             device must be current, as for every call); make that first call before any
  *             stream capture begins.  No cudaMalloc, cudaFree or other allocating routine
- *             is called, then or later.
+ *             is called, then or later.  The address is remembered per device ordinal for
+ *             the life of the process: after a cudaDeviceReset in the same process it is
+ *             stale, so do not call this entry point again after resetting a device.
  *   Sharing   all calls on a device use the same array and it keeps the previous call's
  *             contents.  Nothing needs clearing (every entry that is read is written first
  *             by the same call), but two calls that overlap in time on one GPU, e.g. on
@@ -193,7 +195,9 @@ int rode_spmm_f64_hot(int m1, int m2, int k, int n, const double *values, const 
  * SDDMM:  out[e] = values[e] * dot(lhs[row(e), 0:k], rhs[col(e), 0:k]) for every stored e.
  *
  * Replaces RoDeSDDMM_n32 / RoDeSDDMM_n128 (RoDe_SDDMM/RoDeSddmm.h:4-9, launchers
- * RoDe_SDDMM/RoDeSddmm.cu:496-545).  k in {32, 64, 128} (the reference has 32 and 128);
+ * RoDe_SDDMM/RoDeSddmm.cu:496-545).  k: any multiple of 4 up to 256 (the reference has 32
+ * and 128; here 32, 64 and 128 have kernels of their own shape, every other k runs a
+ * 32-lane x 2-vector form with the vectors beyond the row's end masked);
  * lhs is [M x k], rhs is [n x k], both row-major; out is fp32[nnz] aligned with values.
  * Block segments run on stream1, pure-residue rows on stream2.  A null stream is the
  * default stream (the reference silently skips a kernel whose stream handle is null,

@@ -31,6 +31,12 @@ int fail(int status, const char *fmt, ...);
                                 cudaGetErrorString(rode_err_));                             \
     } while (0)
 
+// RoDe_preprocess without the end sentinel (rode_preprocess.cu); tile_scratch holds
+// rode_preprocess_workspace_bytes(M) bytes.
+int preprocess_reference_signature(int seg_len, int k_block, int vec_len, int M, const int *row_ptr,
+                                   int *block_r_ind, int *st_off, int *residue_r_ind, int *n_blk, int *n_res,
+                                   void *tile_scratch);
+
 inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<size_t>(p) % a) == 0; }
 
 // ---------------------------------------------------------------------------------------
@@ -95,10 +101,15 @@ __device__ __forceinline__ V ld_dense(const V *p) {
 struct GatherPolicy {
     unsigned long long hot, cold;
 };
-__device__ __forceinline__ GatherPolicy make_gather_policy() {
+// steer = false (the bitmap's flag word says that marks would not help on this matrix): both
+// classes of rows get the normal priority, i.e. the kernel behaves like the unhinted one.
+__device__ __forceinline__ GatherPolicy make_gather_policy(bool steer) {
     GatherPolicy p;
+    unsigned long long normal;
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p.hot));
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p.cold));
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(normal));
+    if (!steer) p.hot = p.cold = normal;
     return p;
 }
 __device__ __forceinline__ float4 ld_dense_policy(const float4 *p, unsigned long long policy) {

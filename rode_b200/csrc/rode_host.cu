@@ -202,8 +202,8 @@ void RoDe_preprocess(int N_SEG, int blockX, int vecLen, int M, const int *row_pt
     if (rode_preprocess_workspace_bytes(M, &need) != RODE_OK) return;
     void *ws = nullptr;
     if (rode::scratch_for(rode::kPreprocessScratch, nullptr, need, &ws) != RODE_OK) return;
-    rode_preprocess(N_SEG, blockX, vecLen, M, row_ptr, block_r_ind, st_off, residue_r_ind, n_blk, n_res, ws, need,
-                    nullptr);
+    rode::preprocess_reference_signature(N_SEG, blockX, vecLen, M, row_ptr, block_r_ind, st_off, residue_r_ind, n_blk,
+                                         n_res, ws);
 }
 
 void RoDe_preprocess_cpu(int N_SEG, int blockX, int vecLen, int M, const int *row_ptr, int *block_r_ind,

@@ -131,12 +131,12 @@ count_tiles(Params p, int M, const int *__restrict__ row_ptr, int2 *__restrict__
 
 // Single CTA of kScanThreads, kScanPerThread consecutive tiles per thread (8192 tiles, i.e.
 // 8.4 M rows, per pass).  Turns tile totals into exclusive tile offsets (in place) and
-// publishes n_blk, n_res and the end sentinel st_off[n_blk] = row_ptr[M].
+// publishes n_blk, n_res and, if asked to, the end sentinel st_off[n_blk] = row_ptr[M].
 constexpr int kScanThreads = 1024;
 constexpr int kScanPerThread = 8;
 __global__ void __launch_bounds__(kScanThreads)
 scan_tiles(int n_tiles, int M, const int *__restrict__ row_ptr, int2 *__restrict__ tile_totals,
-           int *__restrict__ st_off, int *__restrict__ n_blk, int *__restrict__ n_res) {
+           int *__restrict__ st_off, int *__restrict__ n_blk, int *__restrict__ n_res, bool write_sentinel) {
     __shared__ int smem[2 * (kScanThreads / 32)];
     int carry_b = 0, carry_r = 0;
     for (int base = 0; base < n_tiles; base += kScanThreads * kScanPerThread) {
@@ -165,7 +165,7 @@ scan_tiles(int n_tiles, int M, const int *__restrict__ row_ptr, int2 *__restrict
     if (threadIdx.x == 0) {
         n_blk[0] = carry_b;
         n_res[0] = carry_r;
-        st_off[carry_b] = row_ptr[M];
+        if (write_sentinel) st_off[carry_b] = row_ptr[M];
     }
 }
 
@@ -261,10 +261,12 @@ int check_params(int seg_len, int k_block, int vec_len, int M, const void *row_p
 
 }  // namespace
 
-// Launches the three kernels; `tile_scratch` holds one int2 per tile.
+// Launches the three kernels; `tile_scratch` holds one int2 per tile.  write_sentinel: also
+// store st_off[n_blk] = row_ptr[M] (the C ABI's contract; the reference's device version does
+// not, and its callers size st_off without room for it).
 int launch_preprocess(int seg_len, int k_block, int vec_len, int M, const int *row_ptr, int *block_r_ind,
                       int *st_off, int *residue_r_ind, int *n_blk, int *n_res, int2 *tile_scratch,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, bool write_sentinel = true) {
     const int n_tiles = (M + kTile - 1) / kTile;
     auto pow2 = [](int x) { return (x & (x - 1)) == 0; };
     const bool all_pow2 = pow2(seg_len) && pow2(k_block) && pow2(vec_len);
@@ -277,7 +279,8 @@ int launch_preprocess(int seg_len, int k_block, int vec_len, int M, const int *r
             count_tiles<false><<<n_tiles, kThreads, 0, stream>>>(p, M, row_ptr, tile_scratch);
         RODE_CHECK_LAUNCH("rode::count_tiles");
     }
-    scan_tiles<<<1, kScanThreads, 0, stream>>>(n_tiles, M, row_ptr, tile_scratch, st_off, n_blk, n_res);
+    scan_tiles<<<1, kScanThreads, 0, stream>>>(n_tiles, M, row_ptr, tile_scratch, st_off, n_blk, n_res,
+                                               write_sentinel);
     RODE_CHECK_LAUNCH("rode::scan_tiles");
     if (n_tiles > 0) {
         if (all_pow2)
@@ -292,6 +295,20 @@ int launch_preprocess(int seg_len, int k_block, int vec_len, int M, const int *r
 }
 
 int preprocess_tiles(int M) { return (M + kTile - 1) / kTile; }
+
+// Body of the reference-signature entry point RoDe_preprocess (Preprocess_opt/_preprocess.cu:323-339):
+// default stream, and nothing is written beyond the n_blk segments and n_res residue rows -- the
+// reference's callers allocate nnz / seg_len + M entries for st_off (_preprocess.cu:426-430),
+// which has no room for an end sentinel when every row is a whole number of segments.
+int preprocess_reference_signature(int seg_len, int k_block, int vec_len, int M, const int *row_ptr,
+                                   int *block_r_ind, int *st_off, int *residue_r_ind, int *n_blk, int *n_res,
+                                   void *tile_scratch) {
+    if (int rc = check_params(seg_len, k_block, vec_len, M, row_ptr)) return rc;
+    if (!block_r_ind || !st_off || !residue_r_ind || !n_blk || !n_res)
+        return fail(RODE_ERR_INVALID_ARGUMENT, "RoDe_preprocess: an output pointer is null");
+    return launch_preprocess(seg_len, k_block, vec_len, M, row_ptr, block_r_ind, st_off, residue_r_ind, n_blk, n_res,
+                             static_cast<int2 *>(tile_scratch), nullptr, /*write_sentinel=*/false);
+}
 
 // ---------------------------------------------------------------------------------------
 // Scratch of rode_preprocess_noalloc: one int2 per tile for up to kNoAllocMaxRows rows,

@@ -81,15 +81,18 @@ __device__ __forceinline__ float reduce_batch(float (&p)[NB], int l, unsigned gm
 
 // kSegments: items are block segments (block_r_ind / st_off); otherwise residue rows
 // (residue_r_ind) without a block part.
-template <int L, int VPL, bool kSegments>
+//
+// kRagged: the dense rows hold row_vecs_arg <= L * VPL vectors (any K that is a multiple of 4
+// up to 4 * L * VPL); vectors beyond the row's end are not loaded and count as zeros.
+template <int L, int VPL, bool kSegments, bool kRagged = false>
 __global__ void __launch_bounds__(32)
 sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, const int *__restrict__ st_off,
             const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
             const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,
-            float *__restrict__ out) {
+            float *__restrict__ out, int row_vecs_arg) {
     constexpr int G = 32 / L;
     constexpr int kBatch = kLoadsInFlight / VPL;  // nonzeros per batch
-    constexpr size_t kRowVecs = L * VPL;          // float4 per dense row (K / 4)
+    const size_t kRowVecs = kRagged ? static_cast<size_t>(row_vecs_arg) : L * VPL;  // float4 per dense row (K / 4)
     constexpr int kAlign = 4;             // vec_len of the preprocessing
     constexpr int kBlockK = 32;           // k_block of the preprocessing
     __shared__ int s_end[32];             // stream position where item j ends
@@ -157,6 +160,12 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
 
     const float4 *lhs_lane = reinterpret_cast<const float4 *>(lhs) + l;
     const float4 *rhs_lane = reinterpret_cast<const float4 *>(rhs) + l;
+    // vector v of this lane lies inside the dense row
+    auto inside = [&](int v) { return !kRagged || static_cast<size_t>(l + v * L) < kRowVecs; };
+    auto load_lhs = [&](int item, int v) {
+        return inside(v) ? __ldg(lhs_lane + static_cast<size_t>(s_row[item]) * kRowVecs + v * L)
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
 
     // ---- item the group is in, its lhs slice, and the next item's (prefetched) --------------------
     // first item whose end lies beyond p0 = number of items that end at or before p0
@@ -176,9 +185,9 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
     float4 a_cur[VPL], a_nxt[VPL];
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-        a_cur[v] = __ldg(lhs_lane + static_cast<size_t>(s_row[cur]) * kRowVecs + v * L);
+        a_cur[v] = load_lhs(cur, v);
         a_nxt[v] = a_cur[v];
-        if (nxt >= 0) a_nxt[v] = __ldg(lhs_lane + static_cast<size_t>(s_row[nxt]) * kRowVecs + v * L);
+        if (nxt >= 0) a_nxt[v] = load_lhs(nxt, v);
     }
 
     int e_cur, c_cur, e_nxt, c_nxt;
@@ -203,7 +212,7 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
 #pragma unroll
                     for (int v = 0; v < VPL; ++v) {
                         bb[u][v] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (t < cnt) bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc) * kRowVecs + v * L);
+                        if (t < cnt && inside(v)) bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc) * kRowVecs + v * L);
                     }
                 }
                 float p[kBatch];
@@ -226,8 +235,7 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
 #pragma unroll
                         for (int v = 0; v < VPL; ++v) {
                             a_cur[v] = a_nxt[v];
-                            if (nxt >= 0)
-                                a_nxt[v] = __ldg(lhs_lane + static_cast<size_t>(s_row[nxt]) * kRowVecs + v * L);
+                            if (nxt >= 0) a_nxt[v] = load_lhs(nxt, v);
                         }
                     }
                     float d = 0.f;
@@ -355,16 +363,39 @@ int launch_k(int m1, int m2, int seg_cap, const int *block_r_ind, const int *res
             RODE_CHECK_LAUNCH("rode::sddmm_block");
         } else {
             const int per = items_per_warp(m1, seg_cap);
-            sddmm_items<L, VPL, true><<<(m1 + per - 1) / per, 32, 0, s1>>>(m1, per, block_r_ind, st_off,
-                                                                            row_offsets, col, values, lhs, rhs, out);
+            sddmm_items<L, VPL, true><<<(m1 + per - 1) / per, 32, 0, s1>>>(m1, per, block_r_ind, st_off, row_offsets,
+                                                                            col, values, lhs, rhs, out, L * VPL);
             RODE_CHECK_LAUNCH("rode::sddmm_items<segments>");
         }
     }
     if (m2 > 0) {
         const int per = items_per_warp(m2, 32);
-        sddmm_items<L, VPL, false><<<(m2 + per - 1) / per, 32, 0, s2>>>(m2, per, residue_r_ind, nullptr,
-                                                                         row_offsets, col, values, lhs, rhs, out);
+        sddmm_items<L, VPL, false><<<(m2 + per - 1) / per, 32, 0, s2>>>(m2, per, residue_r_ind, nullptr, row_offsets,
+                                                                         col, values, lhs, rhs, out, L * VPL);
         RODE_CHECK_LAUNCH("rode::sddmm_items<rows>");
+    }
+    return RODE_OK;
+}
+
+// Any other K that is a multiple of 4, up to 256: 32 lanes x 2 vectors per lane, vectors beyond
+// the row's end masked.  Both item lists run through sddmm_items (a few segments per warp when
+// segments are long).
+int launch_ragged(int m1, int m2, int k, const int *block_r_ind, const int *residue_r_ind, const int *st_off,
+                  const int *row_offsets, const int *col, const float *values, const float *lhs, const float *rhs,
+                  float *out, cudaStream_t s1, cudaStream_t s2) {
+    const int row_vecs = k / 4;
+    if (m1 > 0) {
+        const int per = items_per_warp(m1, 4);
+        sddmm_items<32, 2, true, true><<<(m1 + per - 1) / per, 32, 0, s1>>>(m1, per, block_r_ind, st_off, row_offsets,
+                                                                             col, values, lhs, rhs, out, row_vecs);
+        RODE_CHECK_LAUNCH("rode::sddmm_items<segments, any k>");
+    }
+    if (m2 > 0) {
+        const int per = items_per_warp(m2, 32);
+        sddmm_items<32, 2, false, true><<<(m2 + per - 1) / per, 32, 0, s2>>>(m2, per, residue_r_ind, nullptr,
+                                                                              row_offsets, col, values, lhs, rhs, out,
+                                                                              row_vecs);
+        RODE_CHECK_LAUNCH("rode::sddmm_items<rows, any k>");
     }
     return RODE_OK;
 }
@@ -379,8 +410,8 @@ extern "C" int rode_sddmm_f32(int m1, int m2, int n, int k, const int *block_r_i
     using namespace rode;
     (void)n;
     if (m1 < 0 || m2 < 0) return fail(RODE_ERR_INVALID_ARGUMENT, "sddmm: m1, m2 must be >= 0");
-    if (k != 32 && k != 64 && k != 128)
-        return fail(RODE_ERR_INVALID_ARGUMENT, "sddmm: k = %d unsupported (32, 64 or 128)", k);
+    if (k <= 0 || k % 4 != 0 || k > 256)
+        return fail(RODE_ERR_INVALID_ARGUMENT, "sddmm: k = %d unsupported (a multiple of 4, at most 256)", k);
     if (m1 == 0 && m2 == 0) return RODE_OK;
     if (!row_offsets || !column_indices || !values || !lhs || !rhs || !out)
         return fail(RODE_ERR_INVALID_ARGUMENT, "sddmm: null array");
@@ -398,9 +429,12 @@ extern "C" int rode_sddmm_f32(int m1, int m2, int n, int k, const int *block_r_i
             return launch_k<RODE_SDDMM_SHAPE_64 / 100, RODE_SDDMM_SHAPE_64 % 100>(
                 m1, m2, 4, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values, lhs, rhs, out,
                 stream1, stream2);
-        default:
+        case 128:
             return launch_k<RODE_SDDMM_SHAPE_128 / 100, RODE_SDDMM_SHAPE_128 % 100>(
                 m1, m2, 32, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values, lhs, rhs, out,
                 stream1, stream2);
+        default:
+            return launch_ragged(m1, m2, k, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values,
+                                 lhs, rhs, out, stream1, stream2);
     }
 }

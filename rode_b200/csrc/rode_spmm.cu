@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(32 * W, min_ctas_per_sm(U * VPL) / W)
 spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
            const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
            const int *__restrict__ st_off, const T *__restrict__ B, T *__restrict__ C, T *__restrict__ partial,
-           const unsigned *__restrict__ hot) {
+           const unsigned *__restrict__ hot, int hot_flag_word) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
     constexpr int G = 32 / L;             // lane groups, each takes every G-th nonzero
@@ -143,7 +143,8 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     // chunk before the column is used, so the lookup adds no exposed latency after the first.
     GatherPolicy policy = {};
     if constexpr (kHints) {
-        policy = make_gather_policy();
+        // the word after the bitmap is the library's verdict on this matrix (0: marks would not help)
+        policy = make_gather_policy(__ldg(hot + hot_flag_word) != 0u);
         c_cur = tag_hot(c_cur, hot_word(hot, c_cur));
     }
 
@@ -237,7 +238,15 @@ spmm_fixup(int m1, int n, const int *__restrict__ row_offsets, const int *__rest
         }
     }
     unsigned todo = __ballot_sync(kFull, head);
-    if (todo == 0) return;  // no split row among these 32 segments: nothing to wait for
+    if (todo == 0) {
+        // No split row among these 32 segments: nothing to read from the workspace.  The first
+        // CTA still waits for the block grid, so that this grid as a whole cannot complete
+        // before spmm_block has completed and flushed its stores: whatever the caller enqueues
+        // on the stream afterwards (an event, a copy of C, the next kernel) is then ordered
+        // after the block grid through this grid, as with a plain launch.
+        if (blockIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+        return;
+    }
     // Everything above read only the caller's metadata; the workspace is written by the
     // preceding spmm_block grid: wait for it (no-op when launched without the attribute).
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -577,7 +586,7 @@ int launch_rows(int m2, int n, const T *values, const int *col, const int *row_o
                 const T *B, T *C, cudaStream_t s2);
 
 template <typename T, int L, int VPL, int RL, int RVPL>
-int launch_shape(int m1, int m2, int n, const T *values, const int *col, const int *row_offsets,
+int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, const int *row_offsets,
                  const int *block_r_ind, const int *residue_r_ind, const int *st_off, const T *B, T *C,
                  T *partial, const unsigned *hot, cudaStream_t s1, cudaStream_t s2) {
     static_assert(L * VPL == RL * RVPL, "block and residue kernels must cover the same tile");
@@ -600,17 +609,17 @@ int launch_shape(int m1, int m2, int n, const T *values, const int *col, const i
         if constexpr (L == 32 && VPL == 1) {
             if (hot && !small_grid) {
                 spmm_block<T, L, VPL, U, kCtaWarps, true><<<grid, kCtaThreads, 0, s1>>>(
-                    m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, hot);
+                    m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, hot, (k + 31) / 32);
                 launched = true;
             }
         }
         if (launched) {
         } else if (small_grid && USmall > U) {
             spmm_block<T, L, VPL, USmall, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
-                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr);
+                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0);
         } else {
             spmm_block<T, L, VPL, U, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
-                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr);
+                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0);
         }
         RODE_CHECK_LAUNCH("rode::spmm_block");
         // fix-up as a programmatic dependent of spmm_block: its launch latency and its
@@ -671,8 +680,10 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
          const int *block_r_ind, const int *residue_r_ind, const int *st_off, const T *B, T *C, void *workspace,
          size_t workspace_bytes, const unsigned *hot, rode_stream_t stream1, rode_stream_t stream2) {
     constexpr int kLen = Vec16<T>::kLen;
-    (void)k;
     if (m1 < 0 || m2 < 0 || n <= 0) return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: m1, m2 >= 0 and n > 0 required");
+    if (hot != nullptr && k <= 0)
+        return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: k (the number of columns the bitmap covers) must be positive "
+                                               "when hot_columns is given");
     if (n % (8 * kLen) != 0)
         return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: n = %d is not a multiple of %d", n, 8 * kLen);
     if (m1 == 0 && m2 == 0) return RODE_OK;
@@ -695,7 +706,7 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
     // Widest tile (32, 16 or 8 vectors of 16 bytes) that divides the row.
 #define RODE_LAUNCH(shape, rows_shape)                                                                        \
     launch_shape<T, (shape) / 100, (shape) % 100, (rows_shape) / 100, (rows_shape) % 100>(                     \
-        m1, m2, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, hot, stream1, \
+        m1, m2, k, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, hot, stream1, \
         stream2)
     const int vecs = n / kLen;
     if (vecs % 32 == 0 && RODE_SPMM_MAX_TILE_VECS >= 32) return RODE_LAUNCH(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32);

@@ -26,17 +26,25 @@ class RoDeCSR:
     block_indices, st_offsets, residue_indices, m1, m2``.
     """
 
-    # (seg_length, k_block, vec_len) per hidden width, as in rode_sddmm.py:35-38; 64 is new.
+    # (seg_length, k_block, vec_len) per hidden width, as in rode_sddmm.py:35-38 (32 and 128);
+    # every other width (any multiple of 4 up to 256, which the reference does not serve) uses
+    # the long segments of width 32.
     CONFIGS = {
         32: {"seg_length": 512, "k_block": 32, "vec_len": 4},
         64: {"seg_length": 512, "k_block": 32, "vec_len": 4},
         128: {"seg_length": 32, "k_block": 32, "vec_len": 4},
     }
+    MAX_K = 256
+
+    @classmethod
+    def config_for(cls, k: int) -> dict:
+        if k <= 0 or k % 4 != 0 or k > cls.MAX_K:
+            raise ValueError(f"k must be a multiple of 4, at most {cls.MAX_K}, got {k}")
+        return cls.CONFIGS.get(k, cls.CONFIGS[32])
 
     def __init__(self, row_offsets: torch.Tensor, column_indices: torch.Tensor, values: torch.Tensor,
                  device: torch.device, m: int, n: int, k: int = 128):
-        if k not in self.CONFIGS:
-            raise ValueError(f"k must be 32, 64 or 128, got {k}")
+        self.config_for(k)
         self.m = m
         self.n = n
         self.k = k
@@ -53,7 +61,7 @@ class RoDeCSR:
         self._preprocess()
 
     def _preprocess(self):
-        config = self.CONFIGS[self.k]
+        config = self.config_for(self.k)
         with torch.cuda.device(self.device):
             blk, st, res, m1, m2 = rode_sddmm_cuda.preprocess(
                 self.row_offsets, self.nnz, config["seg_length"], config["k_block"], config["vec_len"])
@@ -119,7 +127,7 @@ def rode_spmm(sparse_matrix: RoDeCSR, dense: torch.Tensor, hints: bool = True) -
     ``hints``: gather popular columns' rows with an L2 policy that keeps them resident
     (same results, fewer DRAM bytes on skewed matrices).  The popularity bitmap is built on
     the first call for a given width and cached on ``sparse_matrix``."""
-    if sparse_matrix.CONFIGS[sparse_matrix.k]["k_block"] != 32:
+    if sparse_matrix.config_for(sparse_matrix.k)["k_block"] != 32:
         raise ValueError("SpMM needs k_block = 32 metadata")
     if dense.dim() != 2 or dense.shape[0] != sparse_matrix.n:
         raise ValueError(f"dense must be ({sparse_matrix.n}, width), got {tuple(dense.shape)}")

@@ -110,7 +110,8 @@ torch::Tensor py_sddmm_forward(torch::Tensor block_indices, torch::Tensor residu
     RODE_CHECK_FLOAT(rhs_matrix);
 
     const int k = static_cast<int>(lhs_matrix.size(1));
-    TORCH_CHECK(k_version == 32 || k_version == 64 || k_version == 128, "k_version must be 32, 64 or 128");
+    TORCH_CHECK(k_version > 0 && k_version % 4 == 0 && k_version <= 256,
+                "k_version must be a multiple of 4, at most 256");
     TORCH_CHECK(k == k_version, "k dimension must match k_version");
     TORCH_CHECK(lhs_matrix.size(0) == m, "lhs_matrix rows must equal m");
     TORCH_CHECK(rhs_matrix.size(0) == n, "rhs_matrix rows must equal n");

@@ -94,11 +94,11 @@ int main() {
     CHECK(cudaMemcpy(counts, d_cnt, sizeof(counts), cudaMemcpyDeviceToHost));
     std::vector<int> blk2(m1 + 1), st2(m1 + 1), res2(m2 + 1);
     CHECK(cudaMemcpy(blk2.data(), d_blk2, sizeof(int) * m1, cudaMemcpyDeviceToHost));
-    CHECK(cudaMemcpy(st2.data(), d_st2, sizeof(int) * (m1 + 1), cudaMemcpyDeviceToHost));
+    CHECK(cudaMemcpy(st2.data(), d_st2, sizeof(int) * m1, cudaMemcpyDeviceToHost));
     CHECK(cudaMemcpy(res2.data(), d_res2, sizeof(int) * m2, cudaMemcpyDeviceToHost));
     bool same = counts[0] == m1 && counts[1] == m2;
     for (int i = 0; i < m1 && same; ++i) same = blk2[i] == blk[i] && st2[i] == st[i];
-    same = same && st2[m1] == st[m1];
+    // (the device version writes no end sentinel st_off[m1], like the reference's)
     for (int i = 0; i < m2 && same; ++i) same = res2[i] == res[i];
 
     cudaStream_t s1, s2;

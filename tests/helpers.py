@@ -9,7 +9,26 @@ REL_TOL = 1e-5
 ABS_TOL = 1e-6
 
 
+def tolerance_stats(got, truth, abs_scale=None):
+    """How much of the tolerance a result uses.  Returns a dict with
+    ``worst_ratio``  max over elements of err / allowed (allowed = the rule of
+                     assert_close_to_truth; <= 1 means the check passes),
+    ``literal_fail`` number of elements that break the literal rule err <= max(1e-5 |truth|, 1e-6),
+                     i.e. the rule without the magnitude-scaled floor,
+    ``elements``     number of elements compared, ``max_err`` the largest absolute error."""
+    got = np.asarray(got, dtype=np.float64)
+    truth = np.asarray(truth, dtype=np.float64)
+    err = np.abs(got - truth)
+    floor = ABS_TOL if abs_scale is None else np.maximum(ABS_TOL, 2.0 ** -22 * np.asarray(abs_scale, np.float64))
+    allowed = np.maximum(REL_TOL * np.abs(truth), floor)
+    literal = np.maximum(REL_TOL * np.abs(truth), ABS_TOL)
+    return {"worst_ratio": float((err / allowed).max()) if err.size else 0.0,
+            "literal_fail": int((err > literal).sum()), "elements": int(err.size),
+            "max_err": float(err.max()) if err.size else 0.0}
+
+
 def assert_close_to_truth(got, truth, abs_scale=None, what=""):
+    """Checks the tolerance rule above and returns tolerance_stats() of the comparison."""
     got = np.asarray(got, dtype=np.float64)
     truth = np.asarray(truth, dtype=np.float64)
     assert got.shape == truth.shape, f"{what}: shape {got.shape} vs {truth.shape}"
@@ -22,6 +41,7 @@ def assert_close_to_truth(got, truth, abs_scale=None, what=""):
         raise AssertionError(
             f"{what}: {bad.sum()} of {bad.size} elements out of tolerance; worst at flat index {i}: "
             f"got {got.flat[i]!r}, truth {truth.flat[i]!r}, err {err.flat[i]:.3e}")
+    return tolerance_stats(got, truth, abs_scale)
 
 
 def spmm_abs_scale(row_ptr, col, val, B):

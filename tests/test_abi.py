@@ -60,7 +60,8 @@ def test_argument_errors_are_reported_not_raised_by_cuda(built_library):
     assert lib.rode_preprocess(512, 32, 4, 5000, 16, 16, 16, 16, 16, 16, 16, 8, None) == capi.RODE_ERR_WORKSPACE
     # unsupported widths
     assert lib.rode_spmm_f32(1, 1, 8, 20, 16, 16, 16, 16, 16, 16, 16, 16, None, 0, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
-    assert lib.rode_sddmm_f32(1, 1, 8, 48, 16, 16, 16, 16, 16, 16, 16, 16, 16, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
+    assert lib.rode_sddmm_f32(1, 1, 8, 50, 16, 16, 16, 16, 16, 16, 16, 16, 16, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
+    assert lib.rode_sddmm_f32(1, 1, 8, 260, 16, 16, 16, 16, 16, 16, 16, 16, 16, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
     # misaligned dense operands (16-byte alignment is part of the contract)
     assert lib.rode_spmm_f32(1, 1, 8, 32, 16, 16, 16, 16, 16, 16, 24, 16, None, 0, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
     assert b"aligned" in lib.rode_last_error()

@@ -87,6 +87,30 @@ def test_spmm_with_hints_is_bit_identical(oracle_cpu, dtype):
                               spmm_abs_scale(srp, scol, sval, B.numpy()), "hinted spmm")
 
 
+def test_bitmap_with_a_cleared_flag_is_harmless_through_the_c_abi(oracle_cpu):
+    """A caller that hands a bitmap straight to rode_spmm_f32_hot without reading its flag
+    word: when the library judged the marks useless (flag 0) the kernel gives every row the
+    normal cache priority; either way the result is the plain entry point's, bit for bit."""
+    A = W.rmat(scale=19)
+    d, meta = gpu_inputs(A)
+    assert meta.m1 > 2 * 32 * 148                    # large enough for the hinted kernel to be chosen
+    n, row_bytes = 128, 512
+    bits, flag, bitmap = _bitmap(d.col, A.n, row_bytes, 20000 * row_bytes)
+    assert flag == 1
+    B = W.dense(A.n, n, seed=9).cuda()
+    plain = capi.spmm(meta, d.row_ptr, d.col, d.val, B)
+    cleared = bitmap.clone()
+    cleared[-1] = 0
+    for bm in (bitmap, cleared):
+        got = capi.spmm(meta, d.row_ptr, d.col, d.val, B, hot=bm)
+        torch.cuda.synchronize()
+        assert torch.equal(got, plain)
+    with pytest.raises(capi.RodeError):              # the bitmap's length is derived from k
+        capi.spmm_raw(torch.float32, meta.m1, meta.m2, 0, n, d.val.data_ptr(), d.col.data_ptr(), d.row_ptr.data_ptr(),
+                      meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(), meta.st_off.data_ptr(),
+                      B.data_ptr(), plain.data_ptr(), None, 0, hot=bitmap.data_ptr())
+
+
 def test_bad_arguments_are_rejected():
     col = torch.zeros(8, dtype=torch.int32, device="cuda")
     bitmap = torch.zeros(4, dtype=torch.int32, device="cuda")

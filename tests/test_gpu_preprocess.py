@@ -73,23 +73,38 @@ def test_gpu_preprocess_more_tiles_than_one_scan_pass(oracle_cpu):
 
 
 def test_reference_signature_entry_point(oracle_cpu):
-    """RoDe_preprocess(N_SEG, blockX, vecLen, M, device pointers...) as the reference declares it."""
+    """RoDe_preprocess(N_SEG, blockX, vecLen, M, device pointers...) as the reference declares
+    it, with buffers sized the way the reference's callers size them
+    (Preprocess_opt/_preprocess.cu:426-432: nnz / N_SEG + M entries, M for the residue list)
+    plus guard words: like the reference's device version it writes the n_blk segments and the
+    n_res rows and nothing else -- in particular no end sentinel st_off[n_blk]."""
     lib = capi.load()
     fn = getattr(lib, capi.CPP_SYMBOLS["RoDe_preprocess"])
     fn.restype = None
-    A = W.pareto_rows(m=50000, n=50000, cap=20000, device="cuda")
-    cap = capi.preprocess_capacity(512, 4, A.m, A.nnz)
-    blk = torch.full((cap,), -1, dtype=torch.int32, device="cuda")
-    st = torch.full((cap + 1,), -1, dtype=torch.int32, device="cuda")
-    res = torch.full((A.m,), -1, dtype=torch.int32, device="cuda")
-    cnt = torch.zeros(2, dtype=torch.int32, device="cuda")
-    torch.cuda.synchronize()
     vp = ctypes.c_void_p
-    fn(512, 32, 4, A.m, vp(A.row_ptr.data_ptr()), vp(blk.data_ptr()), vp(st.data_ptr()), vp(res.data_ptr()),
-       vp(cnt.data_ptr()), vp(cnt.data_ptr() + 4))
-    torch.cuda.synchronize()
-    m1, m2 = cnt.cpu().tolist()
-    want = oracle_cpu.preprocess(A.row_ptr.cpu().numpy(), 512, 32, 4)
-    _same((blk[:m1].cpu().numpy(), st[: m1 + 1].cpu().numpy(), res[:m2].cpu().numpy(), m1, m2), want)
-    # nothing is written past the counts (st_off[m1] is the sentinel)
-    assert bool((blk[m1:] == -1).all()) and bool((st[m1 + 1:] == -1).all()) and bool((res[m2:] == -1).all())
+    guard = 8
+    # second case: fewer nonzeros than one segment and every row at least 32 long, so n_blk
+    # equals the reference-sized capacity nnz / N_SEG + M and a sentinel would land one past it
+    full_rows = W.CSR(7, 4096, torch.arange(0, 8 * 64, 64, dtype=torch.int32), None, None)
+    for A in (W.pareto_rows(m=50000, n=50000, cap=20000, device="cuda"), full_rows):
+        rp = A.row_ptr.cuda()
+        nnz = int(rp[-1])
+        cap = nnz // 512 + A.m
+        blk = torch.full((cap + guard,), -1, dtype=torch.int32, device="cuda")
+        st = torch.full((cap + guard,), -1, dtype=torch.int32, device="cuda")
+        res = torch.full((A.m + guard,), -1, dtype=torch.int32, device="cuda")
+        cnt = torch.zeros(2, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        fn(512, 32, 4, A.m, vp(rp.data_ptr()), vp(blk.data_ptr()), vp(st.data_ptr()), vp(res.data_ptr()),
+           vp(cnt.data_ptr()), vp(cnt.data_ptr() + 4))
+        torch.cuda.synchronize()
+        m1, m2 = cnt.cpu().tolist()
+        want = oracle_cpu.preprocess(rp.cpu().numpy(), 512, 32, 4)
+        assert (m1, m2) == (want[3], want[4]) and m1 <= cap
+        if A is full_rows:
+            assert m1 == cap
+        assert np.array_equal(blk[:m1].cpu().numpy(), want[0])
+        assert np.array_equal(st[:m1].cpu().numpy(), want[1][:m1])
+        assert np.array_equal(res[:m2].cpu().numpy(), want[2])
+        # nothing is written past the counts
+        assert bool((blk[m1:] == -1).all()) and bool((st[m1:] == -1).all()) and bool((res[m2:] == -1).all())

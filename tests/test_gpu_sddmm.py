@@ -27,7 +27,8 @@ def _run(A, lhs, rhs, k):
 def _check(oracle_cpu, A, lhs, rhs, out, what):
     rp, col, val = A.row_ptr.numpy(), A.col.numpy(), A.val.numpy()
     truth = oracle_cpu.sddmm_f64acc(rp, col, val, lhs.numpy(), rhs.numpy(), threads=oracle_cpu.max_threads())
-    assert_close_to_truth(out.cpu().numpy(), truth, sddmm_abs_scale(rp, col, val, lhs.numpy(), rhs.numpy()), what)
+    return assert_close_to_truth(out.cpu().numpy(), truth,
+                                 sddmm_abs_scale(rp, col, val, lhs.numpy(), rhs.numpy()), what)
 
 
 def test_sddmm_matches_reference_fixtures(golden_dir):
@@ -45,7 +46,7 @@ def test_sddmm_matches_reference_fixtures(golden_dir):
 
 
 @pytest.mark.parametrize("k", [32, 64, 128])
-def test_sddmm_families_against_oracle_and_reference(oracle_cpu, k):
+def test_sddmm_families_against_oracle_and_reference(oracle_cpu, headroom, k):
     fams = {
         "bernoulli": W.bernoulli(),
         "zipf": W.zipf_rows(m=4096, n=4096, cap=4096),
@@ -56,11 +57,16 @@ def test_sddmm_families_against_oracle_and_reference(oracle_cpu, k):
     for name, A in fams.items():
         lhs, rhs = W.dense(A.m, k, seed=5), W.dense(A.n, k, seed=6)
         d, meta, out = _run(A, lhs, rhs, k)
-        _check(oracle_cpu, A, lhs, rhs, out, f"{name} k={k}")
+        stats = _check(oracle_cpu, A, lhs, rhs, out, f"{name} k={k}")
+        config1 = name == "bernoulli" and k == 32
+        if config1:
+            headroom("1 Bernoulli 4096^2 SDDMM K=32 (all elements)", "ours", stats)
         assert torch.equal(out, capi.sddmm(meta, d.row_ptr, d.col, d.val, lhs.cuda(), rhs.cuda()))
         if ref.available() and k in (32, 128) and meta.m1 > 0 and meta.m2 > 0:
             oref = run_reference_sddmm(d, meta, lhs.cuda(), rhs.cuda())
-            _check(oracle_cpu, A, lhs, rhs, oref, f"reference {name} k={k}")
+            stats = _check(oracle_cpu, A, lhs, rhs, oref, f"reference {name} k={k}")
+            if config1:
+                headroom("1 Bernoulli 4096^2 SDDMM K=32 (all elements)", "reference kernels", stats)
 
 
 def test_sddmm_edge_cases(oracle_cpu):
@@ -115,7 +121,7 @@ def test_reference_signature_entry_points(oracle_cpu):
 
 
 @pytest.mark.parametrize("family,k", [("stencil", 64), ("pareto", 32), ("pareto", 128), ("rmat", 64)])
-def test_sddmm_full_size_properties(oracle_cpu, family, k):
+def test_sddmm_full_size_properties(oracle_cpu, headroom, family, k):
     """Full-size matrices: a sample of rows against the oracle, and linearity in lhs."""
     A = {"stencil": lambda: W.stencil27(128, device="cuda"),
          "pareto": lambda: W.pareto_rows(device="cuda"),
@@ -130,9 +136,43 @@ def test_sddmm_full_size_properties(oracle_cpu, family, k):
     rp, col, val, idx = sample_rows_csr(A, rows)
     lh, rh = lhs1[rows].cpu().numpy(), rhs.cpu().numpy()
     truth = oracle_cpu.sddmm_f64acc(rp, col, val, lh, rh, threads=oracle_cpu.max_threads())
-    assert_close_to_truth(out1[torch.from_numpy(idx).cuda()].cpu().numpy(), truth,
-                          sddmm_abs_scale(rp, col, val, lh, rh), f"{family} k={k} sample")
+    scale = sddmm_abs_scale(rp, col, val, lh, rh)
+    idx_d = torch.from_numpy(idx).cuda()
+    what = {"stencil": "3 stencil 128^3", "pareto": "4 Pareto 2^20", "rmat": "R-MAT 22"}[family] + f" SDDMM K={k} (row sample)"
+    headroom(what, "ours", assert_close_to_truth(out1[idx_d].cpu().numpy(), truth, scale, f"{family} k={k} sample"))
+    # the reference's kernels where they can run (K = 32 or 128, both lists non-empty, 32-bit offsets)
+    if ref.available() and k in (32, 128) and meta.m1 > 0 and meta.m2 > 0 and (A.n - 1) * k < 2**29:
+        oref = run_reference_sddmm(A, meta, lhs1, rhs)
+        headroom(what, "reference kernels",
+                 assert_close_to_truth(oref[idx_d].cpu().numpy(), truth, scale, f"{family} k={k} sample, reference"))
+        del oref
     lhs2 = W.dense(A.m, k, device="cuda", seed=9)
     out2 = capi.sddmm(meta, A.row_ptr, A.col, A.val, lhs2, rhs)
     out3 = capi.sddmm(meta, A.row_ptr, A.col, A.val, 2 * lhs1 - lhs2, rhs)
     assert (out3 - (2 * out1 - out2)).abs().max().item() <= 1e-4
+
+
+@pytest.mark.parametrize("k", [4, 36, 96, 160, 192, 252, 256])
+def test_sddmm_other_widths(oracle_cpu, k):
+    """Every K that is a multiple of 4 up to 256 behind the one entry point, on metadata of
+    either segment length (the reference serves 32 and 128 only)."""
+    A = W.pareto_rows(m=3000, n=5000, cap=2500, seed=13)
+    lhs, rhs = W.dense(A.m, k, seed=5), W.dense(A.n, k, seed=6)
+    d = A.to("cuda")
+    for seg in (512, 32):
+        meta = capi.preprocess(d.row_ptr, d.nnz, seg, 32, 4)
+        out0 = torch.full((A.nnz,), float("nan"), device="cuda")
+        out = capi.sddmm(meta, d.row_ptr, d.col, d.val, lhs.cuda(), rhs.cuda(), out=out0)
+        torch.cuda.synchronize()
+        _check(oracle_cpu, A, lhs, rhs, out, f"k={k} seg={seg}")
+
+
+def test_sddmm_rejects_unsupported_widths():
+    A = W.bernoulli(m=64, n=64).to("cuda")
+    meta = capi.preprocess(A.row_ptr, A.nnz)
+    for k in (0, 6, 260):
+        x = torch.zeros((64, max(k, 1)), device="cuda")
+        with pytest.raises(capi.RodeError):
+            capi.sddmm_raw(meta.m1, meta.m2, 64, k, meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(),
+                           meta.st_off.data_ptr(), A.row_ptr.data_ptr(), A.col.data_ptr(), A.val.data_ptr(),
+                           x.data_ptr(), x.data_ptr(), x.data_ptr())

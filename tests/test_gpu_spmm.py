@@ -27,25 +27,30 @@ def _small_families():
 def _check_against_truth(oracle_cpu, A, B_host, C_dev, what):
     rp, col, val = A.row_ptr.numpy(), A.col.numpy(), A.val.numpy()
     truth = oracle_cpu.spmm_f64acc(rp, col, val, B_host, threads=oracle_cpu.max_threads())
-    assert_close_to_truth(C_dev.cpu().numpy(), truth, spmm_abs_scale(rp, col, val, B_host), what)
+    return assert_close_to_truth(C_dev.cpu().numpy(), truth, spmm_abs_scale(rp, col, val, B_host), what)
 
 
 @pytest.mark.parametrize("n", [32, 64, 128])
-def test_spmm_families_against_oracle_and_reference(oracle_cpu, n):
+def test_spmm_families_against_oracle_and_reference(oracle_cpu, headroom, n):
     for name, A in _small_families().items():
         d, meta = gpu_inputs(A)
         B = W.dense(A.n, n, seed=3)
         Bd = B.cuda()
         C = capi.spmm(meta, d.row_ptr, d.col, d.val, Bd)
         torch.cuda.synchronize()
-        _check_against_truth(oracle_cpu, A, B.numpy(), C, f"{name} n={n}")
+        stats = _check_against_truth(oracle_cpu, A, B.numpy(), C, f"{name} n={n}")
+        config1 = name == "bernoulli" and n == 32
+        if config1:
+            headroom("1 Bernoulli 4096^2 SpMM N=32 (all elements)", "ours", stats)
         # deterministic: no floating-point atomics
         C2 = capi.spmm(meta, d.row_ptr, d.col, d.val, Bd)
         assert torch.equal(C, C2)
         # the reference's own kernels on the same inputs (needs both kernels to have work)
         if ref.available() and meta.m1 > 0 and meta.m2 > 0 and n in (32, 128):
             Cref = run_reference_spmm(d, meta, Bd, n)
-            _check_against_truth(oracle_cpu, A, B.numpy(), Cref, f"reference {name} n={n}")
+            stats = _check_against_truth(oracle_cpu, A, B.numpy(), Cref, f"reference {name} n={n}")
+            if config1:
+                headroom("1 Bernoulli 4096^2 SpMM N=32 (all elements)", "reference kernels", stats)
             scale = spmm_abs_scale(A.row_ptr.numpy(), A.col.numpy(), A.val.numpy(), B.numpy())
             assert_close_to_truth(C.cpu().numpy(), Cref.cpu().numpy().astype(np.float64), 2 * scale,
                                   f"ours vs reference {name} n={n}")
@@ -137,18 +142,83 @@ def test_reference_signature_entry_points(oracle_cpu):
         _check_against_truth(oracle_cpu, A, B.numpy(), C, name)
 
 
-def test_spmm_full_size_heavy_tail_config(oracle_cpu):
-    """Config 2 at full size (65536 x 65536 Zipf rows, N = 128): every element checked."""
+def test_reference_signature_double_overloads(oracle_cpu):
+    """The two `double` overloads of RoDeSpmm_n32 / RoDeSpmm_n128 (RoDe_SpMM/RoDeSpmm.h:10-14),
+    called through their mangled names with the reference's argument order."""
+    lib = capi.load()
+    A = W.zipf_rows(m=4096, n=4096, cap=4096)
+    d, meta = gpu_inputs(A)
+    vals = d.val.double()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    vp = ctypes.c_void_p
+    for name, n in (("RoDeSpmm_n32_f64", 32), ("RoDeSpmm_n128_f64", 128), ("RoDeSpmm_n128_f64", 64)):
+        fn = getattr(lib, capi.CPP_SYMBOLS[name])
+        fn.restype = None
+        B = W.dense(A.n, n, seed=2, dtype=torch.float64)
+        Bd = B.cuda()
+        C = torch.zeros((A.m, n), device="cuda", dtype=torch.float64)
+        torch.cuda.synchronize()
+        fn(meta.m1, meta.m2, A.n, n, vp(vals.data_ptr()), vp(d.col.data_ptr()), vp(d.row_ptr.data_ptr()),
+           vp(meta.block_r_ind.data_ptr()), vp(meta.residue_r_ind.data_ptr()), vp(meta.st_off.data_ptr()),
+           vp(Bd.data_ptr()), vp(C.data_ptr()), vp(s1.cuda_stream), vp(s2.cuda_stream))
+        s1.synchronize()
+        s2.synchronize()
+        truth = oracle_cpu.spmm_f64(A.row_ptr.numpy(), A.col.numpy(), A.val.numpy().astype(np.float64), B.numpy())
+        assert np.allclose(C.cpu().numpy(), truth, rtol=1e-12, atol=1e-12), name
+
+
+def test_work_enqueued_after_spmm_sees_the_block_kernel_results():
+    """Stream order after a call without split rows.  The fix-up grid is a programmatic
+    dependent of the block grid and its warps leave early when their segments hold no split
+    row; its first CTA nevertheless waits for the block grid, so the fix-up grid cannot
+    complete, and nothing enqueued behind it can start, before the block grid has finished.
+    Checked with a block grid that runs for milliseconds: an asynchronous copy of C to the
+    host right behind the call, on the same stream, must see every row."""
+    A = W.pareto_rows(cap=500, device="cuda")             # 2^20 rows, none longer than one segment
+    meta = capi.preprocess(A.row_ptr, A.nnz)
+    seg_rows = meta.block_r_ind[: meta.m1].long()
+    assert meta.m1 > 0 and meta.m2 > 0
+    assert int(torch.unique(seg_rows).numel()) == meta.m1  # one segment per row: no split rows
+    n = 128
+    B = W.dense(A.n, n, device="cuda", seed=3)
+    stream = torch.cuda.Stream()
+    host = torch.empty((A.m, n), dtype=torch.float32).pin_memory()
+    done = torch.cuda.Event()
+    for attempt in range(3):
+        C = torch.zeros((A.m, n), device="cuda")
+        host.fill_(float("nan"))
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            capi.spmm(meta, A.row_ptr, A.col, A.val, B, C=C, stream1=stream, stream2=stream)
+            host.copy_(C, non_blocking=True)
+            done.record(stream)
+        done.synchronize()
+        early = host.clone()
+        torch.cuda.synchronize()
+        assert torch.equal(early, C.cpu()), f"attempt {attempt}: the copy overtook the block kernel"
+    want = capi.spmm(meta, A.row_ptr, A.col, A.val, B)     # a second, fully synchronised run
+    torch.cuda.synchronize()
+    assert torch.equal(early, want.cpu())
+
+
+def test_spmm_full_size_heavy_tail_config(oracle_cpu, headroom):
+    """Config 2 at full size (65536 x 65536 Zipf rows, N = 128): every element checked, ours
+    and the reference's own kernels."""
     A = W.zipf_rows(device="cuda")
     meta = capi.preprocess(A.row_ptr, A.nnz)
     B = W.dense(A.n, 128, device="cuda", seed=3)
     C = capi.spmm(meta, A.row_ptr, A.col, A.val, B)
     h = A.to("cpu")
-    _check_against_truth(oracle_cpu, h, B.cpu().numpy(), C, "config 2")
+    what = "2 Zipf 65536^2 SpMM N=128 (all elements)"
+    headroom(what, "ours", _check_against_truth(oracle_cpu, h, B.cpu().numpy(), C, "config 2"))
+    if ref.available() and meta.m1 > 0 and meta.m2 > 0:
+        Cref = run_reference_spmm(A, meta, B, 128)
+        headroom(what, "reference kernels",
+                 _check_against_truth(oracle_cpu, h, B.cpu().numpy(), Cref, "config 2, reference kernels"))
 
 
 @pytest.mark.parametrize("family,n", [("stencil", 64), ("pareto", 128), ("rmat", 128)])
-def test_spmm_full_size_properties(oracle_cpu, family, n):
+def test_spmm_full_size_properties(oracle_cpu, headroom, family, n):
     """Full-size matrices: linearity in B, and exact agreement with the oracle on a sample of
     rows (longest rows, empty rows and a random draw)."""
     A = {"stencil": lambda: W.stencil27(128, device="cuda"),
@@ -165,7 +235,15 @@ def test_spmm_full_size_properties(oracle_cpu, family, n):
     rp, col, val, _ = sample_rows_csr(A, rows)
     Bh = B1.cpu().numpy()
     truth = oracle_cpu.spmm_f64acc(rp, col, val, Bh, threads=oracle_cpu.max_threads())
-    assert_close_to_truth(C1[rows].cpu().numpy(), truth, spmm_abs_scale(rp, col, val, Bh), f"{family} sample")
+    scale = spmm_abs_scale(rp, col, val, Bh)
+    what = {"stencil": "3 stencil 128^3", "pareto": "4 Pareto 2^20", "rmat": "R-MAT 22"}[family] + f" SpMM N={n} (row sample)"
+    headroom(what, "ours", assert_close_to_truth(C1[rows].cpu().numpy(), truth, scale, f"{family} sample"))
+    # the reference's kernels where their preconditions hold (both lists non-empty, 32-bit byte offsets)
+    if ref.available() and meta.m1 > 0 and meta.m2 > 0 and n in (32, 128) and (A.n - 1) * n * 4 < 2**31:
+        Cref = run_reference_spmm(A, meta, B1, n)
+        headroom(what, "reference kernels",
+                 assert_close_to_truth(Cref[rows].cpu().numpy(), truth, scale, f"{family} sample, reference kernels"))
+        del Cref
     # linearity: S(2 B1 - B2) == 2 S B1 - S B2 up to rounding of the combination
     B2 = W.dense(A.n, n, device="cuda", seed=4)
     C2 = capi.spmm(meta, A.row_ptr, A.col, A.val, B2)

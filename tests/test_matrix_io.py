@@ -61,3 +61,15 @@ def test_file_to_gpu_pipeline_and_benchmark(tmp_path, capsys, oracle_cpu):
     assert preprocess_bench.main([str(path), "--iters", "3"]) == 0
     line = capsys.readouterr().out.strip().splitlines()[-1].split(",")
     assert line[0] == "z" and int(line[1]) == 3000 and int(line[2]) == A.nnz and len(line) == 9
+
+
+@pytest.mark.gpu
+def test_row_swizzle_on_the_device_matches_a_stable_host_sort():
+    """The Sputnik-style comparator (Preprocess_opt/_preprocess.cu:71-104) on a device row
+    pointer: rows by decreasing length, ties in row order."""
+    A = W.pareto_rows(m=200000, n=200000, cap=30000, device="cuda", seed=17)
+    order = matrix_io.row_swizzle(A.row_ptr)
+    assert order.is_cuda and order.dtype == torch.int32
+    lens = np.diff(A.row_ptr.cpu().numpy().astype(np.int64))
+    want = np.argsort(-lens, kind="stable")
+    assert np.array_equal(order.cpu().numpy(), want.astype(np.int32))

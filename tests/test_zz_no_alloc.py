@@ -13,14 +13,21 @@ from rode_b200 import capi
 from rode_b200 import workloads as W
 
 
-def _run(entry, A, seg, kb, vec):
-    """Calls one of the two entry points on raw device addresses; returns host copies."""
+def _outputs(A, seg, vec):
     cap = capi.preprocess_capacity(seg, vec, A.m, A.nnz)
-    blk = torch.full((max(cap, 1),), -7, dtype=torch.int32, device="cuda")
-    st = torch.full((cap + 1,), -7, dtype=torch.int32, device="cuda")
-    res = torch.full((max(A.m, 1),), -7, dtype=torch.int32, device="cuda")
-    cnt = torch.zeros(2, dtype=torch.int32, device="cuda")
-    stream = torch.cuda.current_stream()
+    return (torch.full((max(cap, 1),), -7, dtype=torch.int32, device="cuda"),
+            torch.full((cap + 1,), -7, dtype=torch.int32, device="cuda"),
+            torch.full((max(A.m, 1),), -7, dtype=torch.int32, device="cuda"),
+            torch.zeros(2, dtype=torch.int32, device="cuda"))
+
+
+def _run(entry, A, seg, kb, vec, stream=None):
+    """Calls one of the two entry points on raw device addresses; returns host copies."""
+    blk, st, res, cnt = _outputs(A, seg, vec)
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    else:
+        stream.wait_stream(torch.cuda.current_stream())   # the fills above ran on the current stream
     if entry == "noalloc":
         capi.preprocess_noalloc_raw(seg, kb, vec, A.m, A.row_ptr.data_ptr(), blk.data_ptr(), st.data_ptr(),
                                     res.data_ptr(), cnt.data_ptr(), cnt.data_ptr() + 4, stream)
@@ -43,6 +50,36 @@ def test_noalloc_matches_workspace_entry_point_on_two_calls_in_a_row():
         assert got[3] == want[3] and got[3][0] > 0 and got[3][1] > 0
         for g, w in zip(got[:3], want[:3]):
             assert np.array_equal(g, w)       # integer outputs: bit-exact, untouched tails included
+    # the same on a stream of the caller's own
+    side = torch.cuda.Stream()
+    got = _run("noalloc", small, 512, 32, 4, stream=side)
+    want = _run("workspace", small, 512, 32, 4)
+    assert got[3] == want[3] and all(np.array_equal(g, w) for g, w in zip(got[:3], want[:3]))
+
+
+@pytest.mark.gpu
+def test_noalloc_leaves_the_device_memory_as_it_found_it():
+    """The point of the entry point: a call obtains no device memory.  With the outputs
+    allocated beforehand, the free memory the driver reports is the same before and after a
+    call (the first call on the device has already looked up the built-in scratch's address)."""
+    A = W.pareto_rows(m=300000, n=300000, cap=40000, device="cuda", seed=71)
+    blk, st, res, cnt = _outputs(A, 512, 4)
+    stream = torch.cuda.current_stream()
+
+    def call():
+        capi.preprocess_noalloc_raw(512, 32, 4, A.m, A.row_ptr.data_ptr(), blk.data_ptr(), st.data_ptr(),
+                                    res.data_ptr(), cnt.data_ptr(), cnt.data_ptr() + 4, stream)
+        torch.cuda.synchronize()
+
+    call()                                                # set-up call of this device, if none came before
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    for _ in range(3):
+        call()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before                      # nothing obtained from the driver
+    assert torch.cuda.memory_reserved() == reserved_before  # nor from torch's allocator
+    assert cnt.cpu().tolist()[0] > 0
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch(built_library):
