@@ -40,19 +40,38 @@ int preprocess_reference_signature(int seg_len, int k_block, int vec_len, int M,
 inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<size_t>(p) % a) == 0; }
 
 // ---------------------------------------------------------------------------------------
-// Device-side vector types: one 16-byte load per lane for either scalar type.
-template <typename T>
-struct Vec16;
+// Device-side vector types: what one lane loads with a single instruction, 16 bytes
+// (LDG.128) or 32 bytes (the 256-bit loads of sm_100), for either scalar type.
+struct __align__(32) f32x8 {
+    float4 lo, hi;
+};
+struct __align__(32) f64x4 {
+    double2 lo, hi;
+};
+template <typename T, int kBytes>
+struct VecB;
 template <>
-struct Vec16<float> {
+struct VecB<float, 16> {
     using type = float4;
     static constexpr int kLen = 4;
 };
 template <>
-struct Vec16<double> {
+struct VecB<double, 16> {
     using type = double2;
     static constexpr int kLen = 2;
 };
+template <>
+struct VecB<float, 32> {
+    using type = f32x8;
+    static constexpr int kLen = 8;
+};
+template <>
+struct VecB<double, 32> {
+    using type = f64x4;
+    static constexpr int kLen = 4;
+};
+template <typename T>
+using Vec16 = VecB<T, 16>;
 
 #ifdef __CUDACC__
 
@@ -88,11 +107,52 @@ __device__ __forceinline__ void vadd(double2 &a, const double2 &b) {
     a.y += b.y;
 }
 
+__device__ __forceinline__ f32x8 vzero(f32x8 *) { return {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)}; }
+__device__ __forceinline__ f64x4 vzero(f64x4 *) { return {make_double2(0.0, 0.0), make_double2(0.0, 0.0)}; }
+__device__ __forceinline__ void vfma(f32x8 &acc, float s, const f32x8 &b) {
+    vfma(acc.lo, s, b.lo);
+    vfma(acc.hi, s, b.hi);
+}
+__device__ __forceinline__ void vfma(f64x4 &acc, double s, const f64x4 &b) {
+    vfma(acc.lo, s, b.lo);
+    vfma(acc.hi, s, b.hi);
+}
+__device__ __forceinline__ f32x8 vshfl_xor(unsigned mask, const f32x8 &v, int lane_mask) {
+    return {vshfl_xor(mask, v.lo, lane_mask), vshfl_xor(mask, v.hi, lane_mask)};
+}
+__device__ __forceinline__ f64x4 vshfl_xor(unsigned mask, const f64x4 &v, int lane_mask) {
+    return {vshfl_xor(mask, v.lo, lane_mask), vshfl_xor(mask, v.hi, lane_mask)};
+}
+__device__ __forceinline__ void vadd(f32x8 &a, const f32x8 &b) {
+    vadd(a.lo, b.lo);
+    vadd(a.hi, b.hi);
+}
+__device__ __forceinline__ void vadd(f64x4 &a, const f64x4 &b) {
+    vadd(a.lo, b.lo);
+    vadd(a.hi, b.hi);
+}
+
 // Read-only gather of a dense-operand vector: cached in L1 and L2 (rows are re-used by
 // neighbouring rows of the sparse matrix).
 template <typename V>
 __device__ __forceinline__ V ld_dense(const V *p) {
     return __ldg(p);
+}
+// 256-bit read-only loads (sm_100): one instruction and one address per 32 bytes.
+__device__ __forceinline__ f32x8 ld_dense(const f32x8 *p) {
+    f32x8 v;
+    asm("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=f"(v.lo.x), "=f"(v.lo.y), "=f"(v.lo.z), "=f"(v.lo.w), "=f"(v.hi.x), "=f"(v.hi.y), "=f"(v.hi.z),
+          "=f"(v.hi.w)
+        : "l"(p));
+    return v;
+}
+__device__ __forceinline__ f64x4 ld_dense(const f64x4 *p) {
+    f64x4 v;
+    asm("ld.global.nc.v4.f64 {%0, %1, %2, %3}, [%4];"
+        : "=d"(v.lo.x), "=d"(v.lo.y), "=d"(v.hi.x), "=d"(v.hi.y)
+        : "l"(p));
+    return v;
 }
 
 // Gathers steered by column popularity (rode_hot_columns): rows of marked columns are loaded
@@ -124,6 +184,21 @@ __device__ __forceinline__ double2 ld_dense_policy(const double2 *p, unsigned lo
     asm("ld.global.nc.L2::cache_hint.v2.f64 {%0, %1}, [%2], %3;" : "=d"(v.x), "=d"(v.y) : "l"(p), "l"(policy));
     return v;
 }
+__device__ __forceinline__ f32x8 ld_dense_policy(const f32x8 *p, unsigned long long policy) {
+    f32x8 v;
+    asm("ld.global.nc.L2::cache_hint.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8], %9;"
+        : "=f"(v.lo.x), "=f"(v.lo.y), "=f"(v.lo.z), "=f"(v.lo.w), "=f"(v.hi.x), "=f"(v.hi.y), "=f"(v.hi.z),
+          "=f"(v.hi.w)
+        : "l"(p), "l"(policy));
+    return v;
+}
+__device__ __forceinline__ f64x4 ld_dense_policy(const f64x4 *p, unsigned long long policy) {
+    f64x4 v;
+    asm("ld.global.nc.L2::cache_hint.v4.f64 {%0, %1, %2, %3}, [%4], %5;"
+        : "=d"(v.lo.x), "=d"(v.lo.y), "=d"(v.hi.x), "=d"(v.hi.y)
+        : "l"(p), "l"(policy));
+    return v;
+}
 // Word of the popularity bitmap that holds column c, and c with its mark moved into bit 31.
 __device__ __forceinline__ unsigned hot_word(const unsigned *hot, int c) { return __ldg(hot + (c >> 5)); }
 __device__ __forceinline__ int tag_hot(int c, unsigned word) {
@@ -149,6 +224,14 @@ __device__ __forceinline__ double ld_stream(const double *p) { return __ldcs(p);
 template <typename V>
 __device__ __forceinline__ void st_stream(V *p, const V &v) {
     __stcs(p, v);
+}
+__device__ __forceinline__ void st_stream(f32x8 *p, const f32x8 &v) {
+    __stcs(reinterpret_cast<float4 *>(p), v.lo);
+    __stcs(reinterpret_cast<float4 *>(p) + 1, v.hi);
+}
+__device__ __forceinline__ void st_stream(f64x4 *p, const f64x4 &v) {
+    __stcs(reinterpret_cast<double2 *>(p), v.lo);
+    __stcs(reinterpret_cast<double2 *>(p) + 1, v.hi);
 }
 
 // Lane mask of the L-lane group that `lane` belongs to (L a power of two <= 32).

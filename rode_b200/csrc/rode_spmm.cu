@@ -81,7 +81,13 @@ constexpr int kSmallGridWarps = RODE_SPMM_WIDE_ROWS_CTA_WARPS;  // rows (warps) 
 #ifndef RODE_SPMM_MAX_TILE_VECS
 #define RODE_SPMM_MAX_TILE_VECS 32
 #endif
-// 16-byte loads a lane keeps in flight per batch (dense rows per batch = this / VPL).
+// Bytes per load instruction of a lane in the block kernel and the per-row residue kernels:
+// 16 (LDG.128) or 32 (the 256-bit loads of sm_100).  The shapes above are given in 16-byte
+// vectors; with 32-byte loads a lane group has half as many lanes.
+#ifndef RODE_SPMM_VEC_BYTES
+#define RODE_SPMM_VEC_BYTES 16
+#endif
+// 16-byte units a lane keeps in flight per batch (dense rows per batch = this * 16 / bytes per load / VPL).
 constexpr int kLoadsInFlight = 8;
 
 // ---------------------------------------------------------------------------------------
@@ -93,14 +99,14 @@ constexpr int kLoadsInFlight = 8;
 // lane: 8 -> 32 CTAs (64 registers), 12 -> 25 (80), 16 -> 20 (96), more -> no limit.
 constexpr int min_ctas_per_sm(int loads) { return loads <= 8 ? 32 : loads <= 12 ? 25 : loads <= 16 ? 20 : 1; }
 
-template <typename T, int L, int VPL, int U, int W, bool kHints>
-__global__ void __launch_bounds__(32 * W, min_ctas_per_sm(U * VPL) / W)
+template <typename T, int VB, int L, int VPL, int U, int W, bool kHints>
+__global__ void __launch_bounds__(32 * W, min_ctas_per_sm(U * VPL * VB / 16) / W)
 spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
            const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
            const int *__restrict__ st_off, const T *__restrict__ B, T *__restrict__ C, T *__restrict__ partial,
            const unsigned *__restrict__ hot, int hot_flag_word) {
-    using V = typename Vec16<T>::type;
-    constexpr int kLen = Vec16<T>::kLen;
+    using V = typename VecB<T, VB>::type;
+    constexpr int kLen = VecB<T, VB>::kLen;
     constexpr int G = 32 / L;             // lane groups, each takes every G-th nonzero
     constexpr int kSteps = 32 / G;        // nonzeros per group per 32-nonzero chunk
     constexpr int NB = (kSteps + U - 1) / U;
@@ -431,14 +437,15 @@ constexpr int kRowsCtaThreads = RODE_SPMM_ROWS_CTA;
 #define RODE_SPMM_WIDE_ROWS_WAVES 2
 #endif
 
-template <typename T, int L, int VPL>
+template <typename T, int VB, int L, int VPL>
 __global__ void __launch_bounds__(kRowsCtaThreads, 1024 / kRowsCtaThreads)  // 64 registers: 32 warps per SM
 spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
                  const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind,
                  const T *__restrict__ B, T *__restrict__ C) {
-    using V = typename Vec16<T>::type;
-    constexpr int kLen = Vec16<T>::kLen;
-    constexpr int U = (kLoadsInFlight / VPL < L) ? kLoadsInFlight / VPL : L;
+    using V = typename VecB<T, VB>::type;
+    constexpr int kLen = VecB<T, VB>::kLen;
+    constexpr int kInFlight = kLoadsInFlight * 16 / VB / VPL;  // dense rows per batch
+    constexpr int U = (kInFlight < L) ? kInFlight : L;
     constexpr int kAlign = 4;    // vec_len of the preprocessing
     constexpr int kBlockK = 32;  // k_block of the preprocessing
     const long long item_ll = (static_cast<long long>(blockIdx.x) * kRowsCtaThreads + threadIdx.x) / L;
@@ -517,13 +524,13 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
 // every (32 / L)-th nonzero each, so that all gathers of the row are in flight at once (L
 // per group), and a butterfly over the groups adds the partial rows.  Two dependent memory
 // round trips after the row's bounds are known, against up to 32 / L in spmm_rows_simple.
-template <typename T, int L, int VPL>
+template <typename T, int VB, int L, int VPL>
 __global__ void __launch_bounds__(32 * kSmallGridWarps, 1)
 spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
                const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind,
                const T *__restrict__ B, T *__restrict__ C) {
-    using V = typename Vec16<T>::type;
-    constexpr int kLen = Vec16<T>::kLen;
+    using V = typename VecB<T, VB>::type;
+    constexpr int kLen = VecB<T, VB>::kLen;
     constexpr int G = 32 / L;    // lane groups; a group takes at most 32 / G = L nonzeros
     constexpr int kAlign = 4;    // vec_len of the preprocessing
     constexpr int kBlockK = 32;  // k_block of the preprocessing
@@ -581,19 +588,22 @@ spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restric
     }
 }
 
-template <typename T, int L, int VPL>
+template <typename T, int VB, int L, int VPL>
 int launch_rows(int m2, int n, const T *values, const int *col, const int *row_offsets, const int *residue_r_ind,
                 const T *B, T *C, cudaStream_t s2);
 
-template <typename T, int L, int VPL, int RL, int RVPL>
+// Block kernel of shape (VB bytes per load, L lanes, VPL loads per lane) and residue-row kernel
+// of shape (RVB, RL, RVPL); both cover the same column tile.
+template <typename T, int VB, int L, int VPL, int RVB, int RL, int RVPL>
 int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, const int *row_offsets,
                  const int *block_r_ind, const int *residue_r_ind, const int *st_off, const T *B, T *C,
                  T *partial, const unsigned *hot, cudaStream_t s1, cudaStream_t s2) {
-    static_assert(L * VPL == RL * RVPL, "block and residue kernels must cover the same tile");
-    constexpr int kTileWidth = L * VPL * Vec16<T>::kLen;
-    constexpr int U = kLoadsInFlight / VPL;                      // rows per batch, large grids
+    static_assert(L * VPL * VB == RL * RVPL * RVB, "block and residue kernels must cover the same tile");
+    constexpr int kTileWidth = L * VPL * VecB<T, VB>::kLen;
+    constexpr int U = kLoadsInFlight * 16 / VB / VPL;            // rows per batch, large grids
     constexpr int kChunkSteps = L;                               // nonzeros per group per chunk
-    constexpr int USmall = (kChunkSteps * VPL <= 32) ? kChunkSteps : 32 / VPL;  // small grids
+    constexpr int kSmallCap = 32 * 16 / VB;                      // small grids: at most 512 bytes per lane in flight
+    constexpr int USmall = (kChunkSteps * VPL <= kSmallCap) ? kChunkSteps : kSmallCap / VPL;
     const unsigned tiles = static_cast<unsigned>(n / kTileWidth);
     if (m1 > 0) {
         // Fewer warps than two full waves of 32 per SM: the latency of the longest segment
@@ -603,22 +613,22 @@ int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, 
         const bool small_grid = static_cast<long long>(m1) * tiles <= 2LL * 32 * sm_count();
         dim3 grid((m1 + kCtaWarps - 1) / kCtaWarps, tiles);
         bool launched = false;
-        // Popularity hints: block kernel of the 32-lane shape only.  In the residue-row kernel
+        // Popularity hints: block kernel of the 512-byte tile only.  In the residue-row kernel
         // the marks saved DRAM bytes (5.36 -> 4.79 GB on R-MAT scale 23) but the extra registers
         // cost more time than that returned (1.41 -> 1.52 ms).
-        if constexpr (L == 32 && VPL == 1) {
+        if constexpr (L * VPL * VB == 512) {
             if (hot && !small_grid) {
-                spmm_block<T, L, VPL, U, kCtaWarps, true><<<grid, kCtaThreads, 0, s1>>>(
+                spmm_block<T, VB, L, VPL, U, kCtaWarps, true><<<grid, kCtaThreads, 0, s1>>>(
                     m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, hot, (k + 31) / 32);
                 launched = true;
             }
         }
         if (launched) {
         } else if (small_grid && USmall > U) {
-            spmm_block<T, L, VPL, USmall, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
+            spmm_block<T, VB, L, VPL, USmall, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
                 m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0);
         } else {
-            spmm_block<T, L, VPL, U, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
+            spmm_block<T, VB, L, VPL, U, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
                 m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0);
         }
         RODE_CHECK_LAUNCH("rode::spmm_block");
@@ -639,17 +649,17 @@ int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, 
                                          C));
         RODE_CHECK_LAUNCH("rode::spmm_fixup");
     }
-    if (m2 > 0) return launch_rows<T, RL, RVPL>(m2, n, values, col, row_offsets, residue_r_ind, B, C, s2);
+    if (m2 > 0) return launch_rows<T, RVB, RL, RVPL>(m2, n, values, col, row_offsets, residue_r_ind, B, C, s2);
     return RODE_OK;
 }
 
-template <typename T, int L, int VPL>
+template <typename T, int VB, int L, int VPL>
 int launch_rows(int m2, int n, const T *values, const int *col, const int *row_offsets, const int *residue_r_ind,
                 const T *B, T *C, cudaStream_t s2) {
-    constexpr int kTileWidth = L * VPL * Vec16<T>::kLen;
+    constexpr int kTileWidth = L * VPL * VecB<T, VB>::kLen;
     const unsigned tiles = static_cast<unsigned>(n / kTileWidth);
     {
-        if (L == 32 && VPL == 1) {
+        if constexpr (VB == 16 && L == 32 && VPL == 1) {
             // 32 rows per warp when the list is long; fewer (shorter dependent chains, more
             // warps) when the warps would not fill the GPU twice over
             const long long slots = 2LL * 28 * sm_count() * (kCtaThreads / 32);
@@ -662,18 +672,23 @@ int launch_rows(int m2, int n, const T *values, const int *col, const int *row_o
                                                            residue_r_ind, B, C);
         } else if (static_cast<long long>(m2) * tiles <= RODE_SPMM_WIDE_ROWS_WAVES * 32LL * sm_count()) {
             dim3 grid((m2 + kSmallGridWarps - 1) / kSmallGridWarps, tiles);
-            spmm_rows_wide<T, L, VPL><<<grid, 32 * kSmallGridWarps, 0, s2>>>(m2, n, values, col, row_offsets,
-                                                                             residue_r_ind, B, C);
+            spmm_rows_wide<T, VB, L, VPL><<<grid, 32 * kSmallGridWarps, 0, s2>>>(m2, n, values, col, row_offsets,
+                                                                                 residue_r_ind, B, C);
         } else {
             constexpr int kRowsPerCta = kRowsCtaThreads / L;
             dim3 grid((m2 + kRowsPerCta - 1) / kRowsPerCta, tiles);
-            spmm_rows_simple<T, L, VPL><<<grid, kRowsCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets,
-                                                                          residue_r_ind, B, C);
+            spmm_rows_simple<T, VB, L, VPL><<<grid, kRowsCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets,
+                                                                              residue_r_ind, B, C);
         }
         RODE_CHECK_LAUNCH("rode::spmm_rows");
     }
     return RODE_OK;
 }
+
+// A shape given in 16-byte vectors (L * 100 + VPL), re-expressed for 32-byte loads: half the
+// loads per lane where that number is even, else half the lanes.
+constexpr int wide_lanes(int shape) { return (shape % 100) % 2 == 0 ? shape / 100 : shape / 200; }
+constexpr int wide_vpl(int shape) { return (shape % 100) % 2 == 0 ? (shape % 100) / 2 : shape % 100; }
 
 template <typename T>
 int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const int *row_offsets,
@@ -703,16 +718,39 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
         if (!aligned_to(workspace, 16)) return fail(RODE_ERR_WORKSPACE, "spmm: workspace must be 16-byte aligned");
     }
     T *partial = static_cast<T *>(workspace);
-    // Widest tile (32, 16 or 8 vectors of 16 bytes) that divides the row.
-#define RODE_LAUNCH(shape, rows_shape)                                                                        \
-    launch_shape<T, (shape) / 100, (shape) % 100, (rows_shape) / 100, (rows_shape) % 100>(                     \
+    // Widest tile (32, 16 or 8 vectors of 16 bytes) that divides the row.  Shapes are given in
+    // 16-byte vectors; with 32-byte loads (operands 32-byte aligned) a group has half the lanes.
+    // The batched residue kernel of the widest tile (shape 3201) always loads 16 bytes per lane.
+#define RODE_LAUNCH16(shape, rows_shape)                                                                        \
+    launch_shape<T, 16, (shape) / 100, (shape) % 100, 16, (rows_shape) / 100, (rows_shape) % 100>(              \
+        m1, m2, k, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, hot, stream1, \
+        stream2)
+#define RODE_LAUNCH32(shape, rows_shape, rows_bytes)                                                             \
+    launch_shape<T, 32, wide_lanes(shape), wide_vpl(shape), rows_bytes,                                          \
+                 (rows_bytes) == 32 ? wide_lanes(rows_shape) : (rows_shape) / 100,                               \
+                 (rows_bytes) == 32 ? wide_vpl(rows_shape) : (rows_shape) % 100>(                                \
         m1, m2, k, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, hot, stream1, \
         stream2)
     const int vecs = n / kLen;
-    if (vecs % 32 == 0 && RODE_SPMM_MAX_TILE_VECS >= 32) return RODE_LAUNCH(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32);
-    if (vecs % 16 == 0) return RODE_LAUNCH(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16);
-    return RODE_LAUNCH(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8);
-#undef RODE_LAUNCH
+    // 32-byte loads measured no faster than 16-byte ones on any benchmark matrix (the gathers are
+    // bound by bytes through L1/L2, not by load instructions), so the default build does not
+    // instantiate them.
+    if constexpr (RODE_SPMM_VEC_BYTES == 32) {
+        if (aligned_to(B, 32) && aligned_to(C, 32) && aligned_to(workspace, 32)) {
+            if (vecs % 32 == 0 && RODE_SPMM_MAX_TILE_VECS >= 32) {
+                if (RODE_SPMM_ROWS_SHAPE_32 == 3201)
+                    return RODE_LAUNCH32(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32, 16);
+                return RODE_LAUNCH32(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32, 32);
+            }
+            if (vecs % 16 == 0) return RODE_LAUNCH32(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16, 32);
+            return RODE_LAUNCH32(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8, 32);
+        }
+    }
+    if (vecs % 32 == 0 && RODE_SPMM_MAX_TILE_VECS >= 32) return RODE_LAUNCH16(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32);
+    if (vecs % 16 == 0) return RODE_LAUNCH16(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16);
+    return RODE_LAUNCH16(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8);
+#undef RODE_LAUNCH16
+#undef RODE_LAUNCH32
 }
 
 }  // namespace

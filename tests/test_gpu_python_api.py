@@ -24,7 +24,7 @@ def api():
     return rode_sddmm
 
 
-@pytest.mark.parametrize("k", [32, 64, 128])
+@pytest.mark.parametrize("k", [32, 64, 128, 96, 200])
 def test_rode_sddmm_against_torch_sampled_addmm(api, k):
     torch.manual_seed(42)
     dev = torch.device("cuda")
@@ -66,8 +66,9 @@ def test_preprocess_binding_accepts_cpu_and_cuda_row_offsets(api, oracle_cpu):
 def test_argument_checks_mirror_the_reference(api):
     dev = torch.device("cuda")
     S = api.RoDeCSR.from_random(128, 96, 8, dev, k=32)
-    with pytest.raises(ValueError):
-        api.RoDeCSR(S.row_offsets_cpu, S.column_indices, S.values, dev, 128, 96, k=48)
+    for bad_k in (50, 260, 0):     # not a multiple of 4, beyond the widest supported, empty
+        with pytest.raises(ValueError):
+            api.RoDeCSR(S.row_offsets_cpu, S.column_indices, S.values, dev, 128, 96, k=bad_k)
     with pytest.raises(ValueError):
         api.rode_sddmm(S, torch.zeros(128, 64, device=dev), torch.zeros(96, 32, device=dev))
     with pytest.raises(AssertionError):
