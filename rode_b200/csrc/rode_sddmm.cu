@@ -21,6 +21,12 @@
 //    the number of live partials at every step (4 + 2 + 1 exchanges, then a butterfly over
 //    the remaining lanes).  The finished dot products land in the lanes that hold the
 //    matching values, so results are stored coalesced.
+//  * Row mode of the residue-row kernel: a warp whose 32 rows hold at least 6 nonzeros on average
+//    does not form a stream; its lane groups (8 lanes x 2 loads for K = 64) take the rows one
+//    each, neighbouring rows side by side, each row by the plain per-row loop sddmm_one_row.
+//    The warp decides from the row lengths it has just loaded (27-point stencil, K = 64:
+//    1.26 -> 0.81 ms, rhs rows shared by neighbouring rows now hit in L1; power-law rows,
+//    K = 64: 0.51 -> 0.44 ms; graphs with many empty rows keep the stream).
 //  * sddmm_block: where segments are long (K = 32, 64: up to 543 nonzeros) a segment gets a
 //    warp of its own; chunk loads are then plain coalesced loads without any search and the
 //    lhs slice never changes (power-law K = 32: 370 us against 744 us through sddmm_items).
@@ -46,6 +52,20 @@ namespace {
 #endif
 #ifndef RODE_SDDMM_SHAPE_128
 #define RODE_SDDMM_SHAPE_128 3201
+#endif
+// Shape of a lane group in the row-per-group mode of the residue-row kernel (0 = no such mode),
+// and the mean number of nonzeros per row from which a warp uses it.
+#ifndef RODE_SDDMM_ROW_SHAPE_32
+#define RODE_SDDMM_ROW_SHAPE_32 801
+#endif
+#ifndef RODE_SDDMM_ROW_SHAPE_64
+#define RODE_SDDMM_ROW_SHAPE_64 802
+#endif
+#ifndef RODE_SDDMM_ROW_SHAPE_128
+#define RODE_SDDMM_ROW_SHAPE_128 0
+#endif
+#ifndef RODE_SDDMM_ROW_MODE_MIN
+#define RODE_SDDMM_ROW_MODE_MIN 6
 #endif
 #ifndef RODE_SDDMM_LONG_SEGMENTS_BY_WARP
 #define RODE_SDDMM_LONG_SEGMENTS_BY_WARP 1
@@ -79,17 +99,96 @@ __device__ __forceinline__ float reduce_batch(float (&p)[NB], int l, unsigned gm
     return r;
 }
 
+// All nonzeros [begin, end) of ONE row, by the lane group (L lanes x VPL loads per lane) that
+// `lane` belongs to; every lane of the group must call with the same row.  Lane l fetches the
+// pair of nonzero l of a chunk of L one chunk ahead; batches of kLoadsInFlight loads per lane.
+template <int L, int VPL>
+__device__ __forceinline__ void sddmm_one_row(int row, int begin, int end, int lane,
+                                              const int *__restrict__ column_indices,
+                                              const float *__restrict__ values, const float *__restrict__ lhs,
+                                              const float *__restrict__ rhs, float *__restrict__ out) {
+    constexpr int kBatch = (kLoadsInFlight / VPL < L) ? kLoadsInFlight / VPL : L;
+    constexpr size_t kRowVecs = L * VPL;
+    const int l = lane % L;
+    const unsigned gmask = group_mask<L>(lane);
+    const float4 *rhs_lane = reinterpret_cast<const float4 *>(rhs) + l;
+    float4 a[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v)
+        a[v] = __ldg(reinterpret_cast<const float4 *>(lhs) + static_cast<size_t>(row) * kRowVecs + v * L + l);
+    int c_nxt = 0;
+    float v_nxt = 0.f;
+    if (begin + l < end) {
+        c_nxt = ld_stream(column_indices + begin + l);
+        v_nxt = ld_stream(values + begin + l);
+    }
+    for (int base = begin; base < end; base += L) {
+        const int c = c_nxt;
+        const float val = v_nxt;
+        const int e = base + L + l;
+        c_nxt = 0;
+        v_nxt = 0.f;
+        if (e < end) {
+            c_nxt = ld_stream(column_indices + e);
+            v_nxt = ld_stream(values + e);
+        }
+        const int cnt = min(L, end - base);
+        float mine = 0.f;
+#pragma unroll
+        for (int b = 0; b < L / kBatch; ++b) {
+            if (b * kBatch < cnt) {  // uniform inside the group
+                float4 bb[kBatch][VPL];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const int t = b * kBatch + u;
+                    const int cc = __shfl_sync(gmask, c, t, L);
+#pragma unroll
+                    for (int v = 0; v < VPL; ++v) {
+                        bb[u][v] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (t < cnt) bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc) * kRowVecs + v * L);
+                    }
+                }
+                float p[kBatch];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    float d = 0.f;
+#pragma unroll
+                    for (int v = 0; v < VPL; ++v) d = dot4(a[v], bb[u][v], d);
+                    p[u] = d;
+                }
+                const float r = reduce_batch<L, kBatch>(p, l, gmask);
+                const float got = (L == kBatch) ? r : __shfl_sync(gmask, r, (l & (kBatch - 1)) * (L / kBatch), L);
+                if ((l / kBatch) == b) mine = got;
+            }
+        }
+        if (base + l < end) st_stream(out + base + l, val * mine);
+    }
+}
+
 // kSegments: items are block segments (block_r_ind / st_off); otherwise residue rows
 // (residue_r_ind) without a block part.
 //
 // kRagged: the dense rows hold row_vecs_arg <= L * VPL vectors (any K that is a multiple of 4
 // up to 4 * L * VPL); vectors beyond the row's end are not loaded and count as zeros.
-template <int L, int VPL, bool kSegments, bool kRagged = false>
-__global__ void __launch_bounds__(32)
+//
+// LB > 0 (residue rows only): a warp whose rows hold at least row_mode_min nonzeros on average
+// does not form a stream; its 32 / LB lane groups (LB lanes x VPLB loads) take the rows one
+// each, neighbouring rows side by side.  Long residue rows need no balancing over the groups,
+// and rows that share columns (stencils, meshes) then find each other's rhs rows in L1; short
+// and empty rows (graphs) are better served by the stream, which splits the warp's nonzeros
+// evenly.  The warp decides from the row lengths it has just loaded, so no statistic of the
+// matrix has to be passed in.
+#ifdef RODE_SDDMM_ITEMS_MIN_CTAS
+#define RODE_SDDMM_ITEMS_BOUNDS __launch_bounds__(32, RODE_SDDMM_ITEMS_MIN_CTAS)
+#else
+#define RODE_SDDMM_ITEMS_BOUNDS __launch_bounds__(32)
+#endif
+template <int L, int VPL, bool kSegments, bool kRagged = false, int LB = 0, int VPLB = 1>
+__global__ void RODE_SDDMM_ITEMS_BOUNDS
 sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, const int *__restrict__ st_off,
             const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
             const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,
-            float *__restrict__ out, int row_vecs_arg) {
+            float *__restrict__ out, int row_vecs_arg, int row_mode_min) {
     constexpr int G = 32 / L;
     constexpr int kBatch = kLoadsInFlight / VPL;  // nonzeros per batch
     const size_t kRowVecs = kRagged ? static_cast<size_t>(row_vecs_arg) : L * VPL;  // float4 per dense row (K / 4)
@@ -130,6 +229,24 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
     start -= len;
     const unsigned nonempty = __ballot_sync(kFull, len > 0);
     if (total == 0) return;
+    if constexpr (LB > 0 && !kSegments && !kRagged) {
+        static_assert(LB * VPLB == L * VPL, "both lane-group shapes must cover the same dense row");
+        // (full warps of 32 rows only: short lists give a warp fewer rows than it has groups, and
+        // there the stream's even split of the nonzeros is what shortens the dependent chain)
+        if (items_per_warp == 32 && total >= row_mode_min * 32) {  // warp-uniform
+            constexpr int GB = 32 / LB;
+            const int gb = lane / LB;
+            for (int j0 = 0; j0 < items_per_warp; j0 += GB) {
+                const int j = j0 + gb;  // items_per_warp <= 32, a multiple of GB or the tail is empty
+                const int r = __shfl_sync(kFull, row, j & 31);
+                const int b0 = __shfl_sync(kFull, begin, j & 31);
+                const int n0 = __shfl_sync(kFull, len, j & 31);
+                if (j < items_per_warp && n0 > 0)
+                    sddmm_one_row<LB, VPLB>(r, b0, b0 + n0, lane, column_indices, values, lhs, rhs, out);
+            }
+            return;
+        }
+    }
     __syncwarp();
 
     // ---- this group's contiguous part of the stream: [p0, p1) ----------------------------------
@@ -353,7 +470,7 @@ int items_per_warp(int n_items, int cap) {
     return static_cast<int>(per);
 }
 
-template <int L, int VPL>
+template <int L, int VPL, int RL, int RVPL>
 int launch_k(int m1, int m2, int seg_cap, const int *block_r_ind, const int *residue_r_ind, const int *st_off,
              const int *row_offsets, const int *col, const float *values, const float *lhs, const float *rhs,
              float *out, cudaStream_t s1, cudaStream_t s2) {
@@ -364,14 +481,15 @@ int launch_k(int m1, int m2, int seg_cap, const int *block_r_ind, const int *res
         } else {
             const int per = items_per_warp(m1, seg_cap);
             sddmm_items<L, VPL, true><<<(m1 + per - 1) / per, 32, 0, s1>>>(m1, per, block_r_ind, st_off, row_offsets,
-                                                                            col, values, lhs, rhs, out, L * VPL);
+                                                                            col, values, lhs, rhs, out, L * VPL, 0);
             RODE_CHECK_LAUNCH("rode::sddmm_items<segments>");
         }
     }
     if (m2 > 0) {
         const int per = items_per_warp(m2, 32);
-        sddmm_items<L, VPL, false><<<(m2 + per - 1) / per, 32, 0, s2>>>(m2, per, residue_r_ind, nullptr, row_offsets,
-                                                                         col, values, lhs, rhs, out, L * VPL);
+        sddmm_items<L, VPL, false, false, RL, RVPL><<<(m2 + per - 1) / per, 32, 0, s2>>>(
+            m2, per, residue_r_ind, nullptr, row_offsets, col, values, lhs, rhs, out, L * VPL,
+            RODE_SDDMM_ROW_MODE_MIN);
         RODE_CHECK_LAUNCH("rode::sddmm_items<rows>");
     }
     return RODE_OK;
@@ -387,14 +505,14 @@ int launch_ragged(int m1, int m2, int k, const int *block_r_ind, const int *resi
     if (m1 > 0) {
         const int per = items_per_warp(m1, 4);
         sddmm_items<32, 2, true, true><<<(m1 + per - 1) / per, 32, 0, s1>>>(m1, per, block_r_ind, st_off, row_offsets,
-                                                                             col, values, lhs, rhs, out, row_vecs);
+                                                                             col, values, lhs, rhs, out, row_vecs, 0);
         RODE_CHECK_LAUNCH("rode::sddmm_items<segments, any k>");
     }
     if (m2 > 0) {
         const int per = items_per_warp(m2, 32);
         sddmm_items<32, 2, false, true><<<(m2 + per - 1) / per, 32, 0, s2>>>(m2, per, residue_r_ind, nullptr,
                                                                               row_offsets, col, values, lhs, rhs, out,
-                                                                              row_vecs);
+                                                                              row_vecs, 0);
         RODE_CHECK_LAUNCH("rode::sddmm_items<rows, any k>");
     }
     return RODE_OK;
@@ -422,15 +540,18 @@ extern "C" int rode_sddmm_f32(int m1, int m2, int n, int k, const int *block_r_i
     switch (k) {
         // segments per warp in sddmm_items: few when segments are long (512), 32 when short
         case 32:
-            return launch_k<RODE_SDDMM_SHAPE_32 / 100, RODE_SDDMM_SHAPE_32 % 100>(
+            return launch_k<RODE_SDDMM_SHAPE_32 / 100, RODE_SDDMM_SHAPE_32 % 100, RODE_SDDMM_ROW_SHAPE_32 / 100,
+                            RODE_SDDMM_ROW_SHAPE_32 % 100>(
                 m1, m2, 4, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values, lhs, rhs, out,
                 stream1, stream2);
         case 64:
-            return launch_k<RODE_SDDMM_SHAPE_64 / 100, RODE_SDDMM_SHAPE_64 % 100>(
+            return launch_k<RODE_SDDMM_SHAPE_64 / 100, RODE_SDDMM_SHAPE_64 % 100, RODE_SDDMM_ROW_SHAPE_64 / 100,
+                            RODE_SDDMM_ROW_SHAPE_64 % 100>(
                 m1, m2, 4, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values, lhs, rhs, out,
                 stream1, stream2);
         case 128:
-            return launch_k<RODE_SDDMM_SHAPE_128 / 100, RODE_SDDMM_SHAPE_128 % 100>(
+            return launch_k<RODE_SDDMM_SHAPE_128 / 100, RODE_SDDMM_SHAPE_128 % 100, RODE_SDDMM_ROW_SHAPE_128 / 100,
+                            RODE_SDDMM_ROW_SHAPE_128 == 0 ? 1 : RODE_SDDMM_ROW_SHAPE_128 % 100>(
                 m1, m2, 32, block_r_ind, residue_r_ind, st_off, row_offsets, column_indices, values, lhs, rhs, out,
                 stream1, stream2);
         default:
