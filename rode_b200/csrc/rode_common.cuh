@@ -215,6 +215,43 @@ __device__ __forceinline__ V gather(const V *lane_base, int c, size_t row_vecs, 
     }
 }
 
+// U consecutive entries of a shared-memory array, read with 16-byte loads (all lanes of a group
+// read the same address: one broadcast wavefront per load, against one per element with shuffles).
+template <int U>
+__device__ __forceinline__ void ld_shared_run(const int *p, int (&out)[U]) {
+    static_assert(U % 4 == 0, "runs of four");
+#pragma unroll
+    for (int u = 0; u < U; u += 4) {
+        const int4 x = *reinterpret_cast<const int4 *>(p + u);
+        out[u] = x.x;
+        out[u + 1] = x.y;
+        out[u + 2] = x.z;
+        out[u + 3] = x.w;
+    }
+}
+template <int U>
+__device__ __forceinline__ void ld_shared_run(const float *p, float (&out)[U]) {
+    static_assert(U % 4 == 0, "runs of four");
+#pragma unroll
+    for (int u = 0; u < U; u += 4) {
+        const float4 x = *reinterpret_cast<const float4 *>(p + u);
+        out[u] = x.x;
+        out[u + 1] = x.y;
+        out[u + 2] = x.z;
+        out[u + 3] = x.w;
+    }
+}
+template <int U>
+__device__ __forceinline__ void ld_shared_run(const double *p, double (&out)[U]) {
+    static_assert(U % 2 == 0, "runs of two");
+#pragma unroll
+    for (int u = 0; u < U; u += 2) {
+        const double2 x = *reinterpret_cast<const double2 *>(p + u);
+        out[u] = x.x;
+        out[u + 1] = x.y;
+    }
+}
+
 // Streaming read of CSR data (touched once): do not let it displace dense rows in L1.
 __device__ __forceinline__ int ld_stream(const int *p) { return __ldcs(p); }
 __device__ __forceinline__ float ld_stream(const float *p) { return __ldcs(p); }

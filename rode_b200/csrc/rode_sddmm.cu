@@ -67,6 +67,15 @@ namespace {
 #ifndef RODE_SDDMM_ROW_MODE_MIN
 #define RODE_SDDMM_ROW_MODE_MIN 6
 #endif
+// 1: the column indices of a chunk reach the lanes of a group through shared memory (stored
+// once, read as 16-byte broadcast runs); 0: by one shuffle per nonzero.
+#ifndef RODE_SDDMM_COLUMNS_IN_SMEM
+#define RODE_SDDMM_COLUMNS_IN_SMEM 1
+#endif
+// Lane-group sizes L of the stream kernel for which it stages (bit mask: 8 | 16 | 32).
+#ifndef RODE_SDDMM_ITEMS_SMEM_MASK
+#define RODE_SDDMM_ITEMS_SMEM_MASK (8 | 16 | 32)
+#endif
 #ifndef RODE_SDDMM_LONG_SEGMENTS_BY_WARP
 #define RODE_SDDMM_LONG_SEGMENTS_BY_WARP 1
 #endif
@@ -102,12 +111,17 @@ __device__ __forceinline__ float reduce_batch(float (&p)[NB], int l, unsigned gm
 // All nonzeros [begin, end) of ONE row, by the lane group (L lanes x VPL loads per lane) that
 // `lane` belongs to; every lane of the group must call with the same row.  Lane l fetches the
 // pair of nonzero l of a chunk of L one chunk ahead; batches of kLoadsInFlight loads per lane.
-template <int L, int VPL>
+// `stage` = 2 x 32 ints of shared memory owned by this warp (two chunk buffers), `stage_buf` the
+// buffer to use next; both are carried from row to row so that a group never stores into a
+// buffer that one of its lanes may still read.
+template <int L, int VPL, bool kStageAllowed>
 __device__ __forceinline__ void sddmm_one_row(int row, int begin, int end, int lane,
                                               const int *__restrict__ column_indices,
                                               const float *__restrict__ values, const float *__restrict__ lhs,
-                                              const float *__restrict__ rhs, float *__restrict__ out) {
+                                              const float *__restrict__ rhs, float *__restrict__ out, int *stage,
+                                              int &stage_buf) {
     constexpr int kBatch = (kLoadsInFlight / VPL < L) ? kLoadsInFlight / VPL : L;
+    constexpr bool kStage = RODE_SDDMM_COLUMNS_IN_SMEM != 0 && kStageAllowed && (kBatch % 4 == 0);
     constexpr size_t kRowVecs = L * VPL;
     const int l = lane % L;
     const unsigned gmask = group_mask<L>(lane);
@@ -134,18 +148,26 @@ __device__ __forceinline__ void sddmm_one_row(int row, int begin, int end, int l
         }
         const int cnt = min(L, end - base);
         float mine = 0.f;
+        int *my_stage = stage + stage_buf * 32 + (lane - l);  // this group's region of the buffer
+        if constexpr (kStage) {
+            my_stage[l] = c;
+            __syncwarp(gmask);
+            stage_buf ^= 1;
+        }
 #pragma unroll
         for (int b = 0; b < L / kBatch; ++b) {
             if (b * kBatch < cnt) {  // uniform inside the group
                 float4 bb[kBatch][VPL];
+                int cc[kBatch];
+                if constexpr (kStage) ld_shared_run<kBatch>(my_stage + b * kBatch, cc);
 #pragma unroll
                 for (int u = 0; u < kBatch; ++u) {
                     const int t = b * kBatch + u;
-                    const int cc = __shfl_sync(gmask, c, t, L);
+                    if constexpr (!kStage) cc[u] = __shfl_sync(gmask, c, t, L);
 #pragma unroll
                     for (int v = 0; v < VPL; ++v) {
                         bb[u][v] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (t < cnt) bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc) * kRowVecs + v * L);
+                        if (t < cnt) bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc[u]) * kRowVecs + v * L);
                     }
                 }
                 float p[kBatch];
@@ -178,13 +200,14 @@ __device__ __forceinline__ void sddmm_one_row(int row, int begin, int end, int l
 // and empty rows (graphs) are better served by the stream, which splits the warp's nonzeros
 // evenly.  The warp decides from the row lengths it has just loaded, so no statistic of the
 // matrix has to be passed in.
-#ifdef RODE_SDDMM_ITEMS_MIN_CTAS
-#define RODE_SDDMM_ITEMS_BOUNDS __launch_bounds__(32, RODE_SDDMM_ITEMS_MIN_CTAS)
-#else
-#define RODE_SDDMM_ITEMS_BOUNDS __launch_bounds__(32)
+// One-warp CTAs per SM the register allocation must allow: 28 (72 registers).  Left to itself the
+// compiler takes 78-80 registers for K = 64 once the chunk staging is in, and the four warps per
+// SM that costs outweigh what the staging gains; 64 registers (32 CTAs) spill.
+#ifndef RODE_SDDMM_ITEMS_MIN_CTAS
+#define RODE_SDDMM_ITEMS_MIN_CTAS 28
 #endif
 template <int L, int VPL, bool kSegments, bool kRagged = false, int LB = 0, int VPLB = 1>
-__global__ void RODE_SDDMM_ITEMS_BOUNDS
+__global__ void __launch_bounds__(32, kRagged ? 24 : RODE_SDDMM_ITEMS_MIN_CTAS)
 sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, const int *__restrict__ st_off,
             const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
             const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,
@@ -196,6 +219,8 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
     constexpr int kBlockK = 32;           // k_block of the preprocessing
     __shared__ int s_end[32];             // stream position where item j ends
     __shared__ int s_row[32];             // row of item j
+    __shared__ __align__(16) int s_col[2][32];  // column indices of the current chunk, two buffers
+    int stage_buf = 0;
     const int lane = threadIdx.x;
     const int g = lane / L, l = lane % L;
     const unsigned gmask = group_mask<L>(lane);
@@ -242,7 +267,8 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
                 const int b0 = __shfl_sync(kFull, begin, j & 31);
                 const int n0 = __shfl_sync(kFull, len, j & 31);
                 if (j < items_per_warp && n0 > 0)
-                    sddmm_one_row<LB, VPLB>(r, b0, b0 + n0, lane, column_indices, values, lhs, rhs, out);
+                    sddmm_one_row<LB, VPLB, ((RODE_SDDMM_ITEMS_SMEM_MASK) & L) != 0>(r, b0, b0 + n0, lane, column_indices, values, lhs, rhs, out, &s_col[0][0],
+                                            stage_buf);
             }
             return;
         }
@@ -318,18 +344,28 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
         fetch(p0 + (ch + 2) * L + l, e_pre, c_pre, v_pre);
         const int cnt = min(L, p1 - (p0 + ch * L));  // valid nonzeros of this chunk (may be <= 0)
         float mine = 0.f;
+        constexpr bool kStage = RODE_SDDMM_COLUMNS_IN_SMEM != 0 && ((RODE_SDDMM_ITEMS_SMEM_MASK) & L) != 0 && (kBatch % 4 == 0);
+        int *my_stage = &s_col[stage_buf][lane - l];  // this group's region of the chunk buffer
+        if constexpr (kStage) {
+            my_stage[l] = c_cur;
+            __syncwarp();  // every group runs the same number of chunks
+            stage_buf ^= 1;
+        }
 #pragma unroll
         for (int b = 0; b < L / kBatch; ++b) {
             if (b * kBatch < cnt) {  // uniform inside the group; no warp-wide shuffles inside
                 float4 bb[kBatch][VPL];
+                int cc[kBatch];
+                if constexpr (kStage) ld_shared_run<kBatch>(my_stage + b * kBatch, cc);
 #pragma unroll
                 for (int u = 0; u < kBatch; ++u) {
                     const int t = b * kBatch + u;
-                    const int cc = __shfl_sync(gmask, c_cur, t, L);
+                    if constexpr (!kStage) cc[u] = __shfl_sync(gmask, c_cur, t, L);
 #pragma unroll
                     for (int v = 0; v < VPL; ++v) {
                         bb[u][v] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (t < cnt && inside(v)) bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc) * kRowVecs + v * L);
+                        if (t < cnt && inside(v))
+                            bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc[u]) * kRowVecs + v * L);
                     }
                 }
                 float p[kBatch];
@@ -390,6 +426,9 @@ sddmm_block(int m1, const int *__restrict__ block_r_ind, const int *__restrict__
             float *__restrict__ out) {
     constexpr int kBatch = kLoadsInFlight / VPL;
     constexpr size_t kRowVecs = L * VPL;
+    constexpr bool kStage = RODE_SDDMM_COLUMNS_IN_SMEM != 0 && (kBatch % 4 == 0);
+    __shared__ __align__(16) int s_col[2][32];  // column indices of the current chunk, two buffers
+    int stage_buf = 0;
     const int seg = blockIdx.x;
     if (seg >= m1) return;
     const int lane = threadIdx.x;
@@ -427,18 +466,25 @@ sddmm_block(int m1, const int *__restrict__ block_r_ind, const int *__restrict__
         }
         const int cnt = min(32, end - base);
         float mine = 0.f;
+        if constexpr (kStage) {
+            s_col[stage_buf][lane] = c_cur;
+            __syncwarp();
+        }
 #pragma unroll
         for (int b = 0; b < L / kBatch; ++b) {
             if (gbase + b * kBatch < cnt) {  // uniform inside the group
                 float4 bb[kBatch][VPL];
+                int cc[kBatch];
+                if constexpr (kStage) ld_shared_run<kBatch>(&s_col[stage_buf][gbase + b * kBatch], cc);
 #pragma unroll
                 for (int u = 0; u < kBatch; ++u) {
                     const int t = b * kBatch + u;  // nonzero inside the group's part of the chunk
-                    const int cc = __shfl_sync(gmask, c_cur, t, L);
+                    if constexpr (!kStage) cc[u] = __shfl_sync(gmask, c_cur, t, L);
 #pragma unroll
                     for (int v = 0; v < VPL; ++v) {
                         bb[u][v] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (gbase + t < cnt) bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc) * kRowVecs + v * L);
+                        if (gbase + t < cnt)
+                            bb[u][v] = ld_dense(rhs_lane + static_cast<size_t>(cc[u]) * kRowVecs + v * L);
                     }
                 }
                 float p[kBatch];
@@ -459,6 +505,7 @@ sddmm_block(int m1, const int *__restrict__ block_r_ind, const int *__restrict__
         v_cur = v_nxt;
         c_nxt = c_pre;
         v_nxt = v_pre;
+        stage_buf ^= 1;
     }
 }
 

@@ -87,6 +87,13 @@ constexpr int kSmallGridWarps = RODE_SPMM_WIDE_ROWS_CTA_WARPS;  // rows (warps) 
 #ifndef RODE_SPMM_VEC_BYTES
 #define RODE_SPMM_VEC_BYTES 16
 #endif
+// How the (column, value) pairs of a chunk reach the lanes that gather with them: 1 = through
+// shared memory (the chunk is stored once, every lane group reads its run with 16-byte broadcast
+// loads), 0 = by one shuffle per pair and element.  Shuffles and loads share the SM's load/store
+// data path, where a shuffle costs as much as 128 bytes of gathered data.
+#ifndef RODE_SPMM_PAIRS_IN_SMEM
+#define RODE_SPMM_PAIRS_IN_SMEM 1
+#endif
 // 16-byte units a lane keeps in flight per batch (dense rows per batch = this * 16 / bytes per load / VPL).
 constexpr int kLoadsInFlight = 8;
 
@@ -120,6 +127,15 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     if (seg >= m1) return;
     const int lane = threadIdx.x & 31;
     const int g = lane / L, l = lane % L;
+    // Chunk staging (two buffers, so one __syncwarp per chunk orders both the reads after the
+    // writes and the next-but-one chunk's writes after these reads).  The pair of position t
+    // sits at (t % G) * kSteps + t / G: the run of a lane group is contiguous.
+    constexpr bool kStage = RODE_SPMM_PAIRS_IN_SMEM != 0 && (kSteps % U == 0) && (U % 4 == 0);
+    __shared__ __align__(16) int s_col[kStage ? W : 1][2][32];
+    __shared__ __align__(16) T s_val[kStage ? W : 1][2][32];
+    const int warp_in_cta = kStage ? (threadIdx.x >> 5) : 0;
+    const int stage_slot = (lane % G) * kSteps + lane / G;
+    int stage_buf = 0;
 
     const int row = __ldg(block_r_ind + seg);
     const int off = __ldg(st_off + seg);
@@ -167,20 +183,32 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
         }
         unsigned w_nxt = 0;
         if constexpr (kHints) w_nxt = hot_word(hot, c_nxt);
+        if constexpr (kStage) {
+            s_col[warp_in_cta][stage_buf][stage_slot] = c_cur;
+            s_val[warp_in_cta][stage_buf][stage_slot] = v_cur;
+            __syncwarp();
+        }
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
             if (b * U * G >= cnt) break;  // warp-uniform
             V buf[U][VPL];
             T vv[U];
+            int cc[U];
+            if constexpr (kStage) {
+                ld_shared_run<U>(&s_col[warp_in_cta][stage_buf][g * kSteps + b * U], cc);
+                ld_shared_run<U>(&s_val[warp_in_cta][stage_buf][g * kSteps + b * U], vv);
+            }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int t = (b * U + u) * G + g;  // position inside the chunk
-                const int c = __shfl_sync(kFull, c_cur, t & 31);
-                vv[u] = __shfl_sync(kFull, v_cur, t & 31);
+                if constexpr (!kStage) {
+                    cc[u] = __shfl_sync(kFull, c_cur, t & 31);
+                    vv[u] = __shfl_sync(kFull, v_cur, t & 31);
+                }
 #pragma unroll
                 for (int v = 0; v < VPL; ++v) {
                     buf[u][v] = vzero(static_cast<V *>(nullptr));
-                    if (t < cnt) buf[u][v] = gather<kHints>(b_lane + v * L, c, row_vecs, policy);
+                    if (t < cnt) buf[u][v] = gather<kHints>(b_lane + v * L, cc[u], row_vecs, policy);
                 }
             }
 #pragma unroll
@@ -192,6 +220,7 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
         v_cur = v_nxt;
         c_nxt = c_pre;
         v_nxt = v_pre;
+        stage_buf ^= 1;
     }
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
@@ -380,23 +409,42 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
     int pos = 0;
     V acc = vzero(static_cast<V *>(nullptr));
 
+    // chunk staging in shared memory as in spmm_block (one region of L pairs per lane group)
+    constexpr bool kStage = RODE_SPMM_PAIRS_IN_SMEM != 0 && (L % U == 0) && (U % 4 == 0);
+    __shared__ __align__(16) int s_col[2][kStage ? kCtaThreads : 1];
+    __shared__ __align__(16) T s_val[2][kStage ? kCtaThreads : 1];
+    const int stage_base = (threadIdx.x / L) * L;  // first slot of this group's region
+    int stage_buf = 0;
+
     for (int base = 0; base < total; base += L) {
         const int cnt = min(L, total - base);
         int c_pre;
         T v_pre;
         fetch(base + 2 * L + l, c_pre, v_pre);
+        if constexpr (kStage) {
+            s_col[stage_buf][stage_base + l] = c_cur;
+            s_val[stage_buf][stage_base + l] = v_cur;
+            __syncwarp(gmask);
+        }
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
             if (b * U >= cnt) break;  // group-uniform
             V buf[U];
             T vv[U];
+            int cc[U];
+            if constexpr (kStage) {
+                ld_shared_run<U>(&s_col[stage_buf][stage_base + b * U], cc);
+                ld_shared_run<U>(&s_val[stage_buf][stage_base + b * U], vv);
+            }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int t = b * U + u;  // position inside the chunk
-                const int c = __shfl_sync(gmask, c_cur, t, L);
-                vv[u] = __shfl_sync(gmask, v_cur, t, L);
+                if constexpr (!kStage) {
+                    cc[u] = __shfl_sync(gmask, c_cur, t, L);
+                    vv[u] = __shfl_sync(gmask, v_cur, t, L);
+                }
                 buf[u] = vzero(static_cast<V *>(nullptr));
-                if (t < cnt) buf[u] = ld_dense(b_lane + static_cast<size_t>(c) * row_vecs);
+                if (t < cnt) buf[u] = ld_dense(b_lane + static_cast<size_t>(cc[u]) * row_vecs);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -420,6 +468,7 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
         v_cur = v_nxt;
         c_nxt = c_pre;
         v_nxt = v_pre;
+        stage_buf ^= 1;
     }
 }
 
@@ -477,6 +526,13 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
         c_nxt = ld_stream(column_indices + begin + l);
         v_nxt = ld_stream(values + begin + l);
     }
+    // chunk staging in shared memory as in spmm_block (one region of L pairs per lane group; the
+    // groups of a warp run rows of different lengths, so they synchronise by group)
+    constexpr bool kStage = RODE_SPMM_PAIRS_IN_SMEM != 0 && (L % U == 0) && (U % 4 == 0);
+    __shared__ __align__(16) int s_col[2][kStage ? kRowsCtaThreads : 1];
+    __shared__ __align__(16) T s_val[2][kStage ? kRowsCtaThreads : 1];
+    const int stage_base = (threadIdx.x / L) * L;
+    int stage_buf = 0;
     for (int base = begin; base < end; base += L) {
         const int c = c_nxt;
         const T val = v_nxt;
@@ -488,16 +544,26 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
             v_nxt = ld_stream(values + e);
         }
         const int cnt = min(L, end - base);
+        if constexpr (kStage) {
+            s_col[stage_buf][stage_base + l] = c;
+            s_val[stage_buf][stage_base + l] = val;
+            __syncwarp(gmask);
+        }
 #pragma unroll
         for (int t0 = 0; t0 < L; t0 += U) {
             if (t0 >= cnt) break;
             int cc[U];
             T vv[U];
             V bb[U][VPL];
+            if constexpr (kStage) {
+                ld_shared_run<U>(&s_col[stage_buf][stage_base + t0], cc);
+                ld_shared_run<U>(&s_val[stage_buf][stage_base + t0], vv);
+            } else {
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                cc[u] = __shfl_sync(gmask, c, t0 + u, L);
-                vv[u] = __shfl_sync(gmask, val, t0 + u, L);
+                for (int u = 0; u < U; ++u) {
+                    cc[u] = __shfl_sync(gmask, c, t0 + u, L);
+                    vv[u] = __shfl_sync(gmask, val, t0 + u, L);
+                }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u)
@@ -511,6 +577,7 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
 #pragma unroll
                 for (int v = 0; v < VPL; ++v) vfma(acc[v], vv[u], bb[u][v]);
         }
+        stage_buf ^= 1;
     }
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
