@@ -176,3 +176,36 @@ def test_sddmm_rejects_unsupported_widths():
             capi.sddmm_raw(meta.m1, meta.m2, 64, k, meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(),
                            meta.st_off.data_ptr(), A.row_ptr.data_ptr(), A.col.data_ptr(), A.val.data_ptr(),
                            x.data_ptr(), x.data_ptr(), x.data_ptr())
+
+
+@pytest.mark.parametrize("k", [32, 64])
+def test_sddmm_row_mode_every_entry(oracle_cpu, k):
+    """A residue list long enough for the residue kernel to give its warps 32 rows each, with
+    rows of every length from 0 to 31 mixed at random and a ragged last warp: warps whose rows
+    are long take the row mode (one lane group per row), the others the stream; every entry of
+    the result is checked, and a NaN-filled output shows entries written never or twice."""
+    m, n = 520_001, 60_000
+    g = torch.Generator().manual_seed(77)
+    lens = torch.randint(0, 32, (m,), generator=g)
+    lens[torch.rand(m, generator=g) < 0.2] = 0                 # empty rows in between
+    dense_part = slice(100_000, 200_000)                       # a stretch of long rows only
+    lens[dense_part] = torch.randint(20, 32, (100_000,), generator=g)
+    rp = torch.zeros(m + 1, dtype=torch.int64)
+    torch.cumsum(lens, 0, out=rp[1:])
+    nnz = int(rp[-1])
+    # ascending distinct columns per row: a random start plus a stride, modulo nothing (n is large enough)
+    row_of = torch.repeat_interleave(torch.arange(m), lens)
+    pos = torch.arange(nnz) - rp[:-1][row_of]
+    start = torch.randint(0, n - 32 * 40, (m,), generator=g)
+    stride = torch.randint(1, 40, (m,), generator=g)
+    col = (start[row_of] + pos * stride[row_of]).to(torch.int32)
+    val = torch.rand(nnz, generator=g) * 2 - 1
+    A = W.CSR(m, n, rp.to(torch.int32), col, val)
+    lhs, rhs = W.dense(m, k, seed=5), W.dense(n, k, seed=6)
+    d = A.to("cuda")
+    meta = capi.preprocess(d.row_ptr, d.nnz, 512, 32, 4)
+    assert meta.m2 > 31 * 4 * 24 * 148      # enough rows for 32 per warp on a 148-SM part
+    out0 = torch.full((nnz,), float("nan"), device="cuda")
+    out = capi.sddmm(meta, d.row_ptr, d.col, d.val, lhs.cuda(), rhs.cuda(), out=out0)
+    torch.cuda.synchronize()
+    _check(oracle_cpu, A, lhs, rhs, out, f"row mode k={k}")
