@@ -1,6 +1,8 @@
 """bench.py's command line on CPU: the reference arm prints exactly one JSON line with the
-agreed keys (bounded sample, oracle port on the host threads), and the product arm refuses to
-run without a GPU instead of falling back."""
+agreed keys (whole passes over the workload's matrix, oracle port on the host threads, the
+step and warm-up counts it was given), the product arm refuses to run without a GPU instead
+of falling back, and the record of measured DRAM traffic is only used for the kernel sources
+it was captured from."""
 import json
 import os
 import subprocess
@@ -27,7 +29,9 @@ def test_reference_arm_prints_one_json_line(oracle_cpu):
     assert d["impl"] == "reference" and d["unit"] == "GFLOP/s" and d["value"] > 0 and d["higher_is_better"] is True
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
     assert d["e2e"] == {"value": d["value"], "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
-    assert d["config"]["workload"].endswith("spmm_n128") and d["steps"] == 2
+    assert d["config"]["workload"] == "rmat14_spmm_n128" and d["steps"] == 2 and d["warmup"] == 1
+    assert d["config"]["rows"] == 1 << 14 and d["config"]["n"] == 128 and d["config"]["nnz"] > 0
+    assert str(d["config"]["nnz"]) in d["cpu_baseline"]["sample"]      # whole passes over that very matrix
 
 
 def test_reference_arm_uses_all_cores_under_a_launcher_that_sets_omp_threads(oracle_cpu):
@@ -48,3 +52,27 @@ def test_product_arm_needs_a_gpu():
         return
     res = _run("--steps", "1")
     assert res.returncode != 0 and "no CPU path" in (res.stderr + res.stdout)
+
+
+def test_traffic_record_is_tied_to_the_kernel_sources(tmp_path, monkeypatch):
+    sys.path.insert(0, ROOT)
+    import bench
+
+    digest = bench.kernel_source_digest()
+    rec = {"commit": "abc1234", "kernel_source_digest": digest,
+           "captures": {"rmat23_n128_hints": {"kernel": "rode::spmm_block<...>", "launches": 1,
+                                              "dram_bytes_per_launch": 123}}}
+    path = tmp_path / "traffic.json"
+    path.write_text(json.dumps(rec))
+    monkeypatch.setattr(bench, "TRAFFIC_FILE", str(path))
+    value, source = bench.measured_traffic(23, True)
+    assert value == 123 and "abc1234" in source
+    assert bench.measured_traffic(23, False)[0] is None          # no capture of the plain kernel
+    assert bench.measured_traffic(21, True)[0] is None
+    rec["kernel_source_digest"] = "0" * 16                          # the sources changed since the capture
+    path.write_text(json.dumps(rec))
+    value, why = bench.measured_traffic(23, True)
+    assert value is None and "changed" in why
+    monkeypatch.setattr(bench, "TRAFFIC_FILE", str(tmp_path / "missing.json"))
+    assert bench.measured_traffic(23, True)[0] is None
+
