@@ -27,13 +27,18 @@
 //    The warp decides from the row lengths it has just loaded (27-point stencil, K = 64:
 //    1.26 -> 0.81 ms, rhs rows shared by neighbouring rows now hit in L1; power-law rows,
 //    K = 64: 0.51 -> 0.44 ms; graphs with many empty rows keep the stream).
+//  * The column indices of a chunk reach the lanes that gather with them through a small
+//    double-buffered shared-memory tile (stored once per chunk, read as 16-byte broadcast runs)
+//    instead of one shuffle per nonzero: shuffles share the SM's load/store data path with the
+//    gathers (block kernel K = 64 on an R-MAT graph 2.29 -> 2.16 ms, power-law residue rows
+//    K = 32 0.33 -> 0.26 ms).
 //  * sddmm_block: where segments are long (K = 32, 64: up to 543 nonzeros) a segment gets a
 //    warp of its own; chunk loads are then plain coalesced loads without any search and the
 //    lhs slice never changes (power-law K = 32: 370 us against 744 us through sddmm_items).
 //  * One-warp CTAs: a CTA's slot is held until its slowest warp finishes.
 //
 // Per nonzero: 12 B of CSR data/output plus 4*K bytes of rhs (L1/L2/HBM by reuse); per item
-// 4*K bytes of lhs per group that touches it.  No atomics, no workspace.
+// 4*K bytes of lhs per group that touches it.  No atomics, no workspace in global memory.
 #include <climits>
 
 #include "rode_common.cuh"
