@@ -11,8 +11,10 @@
 //    0.99 -> 0.75 ms, N = 64 stencil 0.97 -> 0.75 ms; for 32 vectors no shape beat 32 x 1).
 //    A warp holds G = 32/L lane groups.
 //  * Gathers are issued in batches of 8 independent LDG.128 per lane; the (column,
-//    value) pairs of a chunk of 32 nonzeros are fetched two chunks ahead and handed to the
-//    lanes by shuffles.  Bytes in flight per SM = resident warps x 32 x U x 16 B, so the
+//    value) pairs of a chunk of 32 nonzeros are fetched two chunks ahead, stored once into a
+//    double-buffered shared-memory tile and read by every lane group as 16-byte broadcast runs
+//    (one shuffle per pair element and nonzero costs the SM's load/store data path as much as
+//    128 bytes of gathered data).  Bytes in flight per SM = resident warps x 32 x U x 16 B, so the
 //    kernels are kept at 64 registers (32 one-warp CTAs per SM, ~131 KB in flight).  Two
 //    register buffers per lane (software pipelining) were measured and rejected: 168
 //    registers cut the resident warps to 12 and the time went up by 30 %.
