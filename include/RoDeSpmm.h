@@ -15,9 +15,9 @@
  * a void function: they are recorded and can be read with rode_last_error().
  *
  * Rows cut into several segments are summed through a workspace that the library keeps for
- * these entry points: one growable device buffer per (device, stream1), allocated on the
- * first call on that stream (cudaMalloc) and re-used afterwards.  Calls on the same stream1
- * are ordered by the stream and share the buffer; calls on different streams get buffers of
+ * these entry points: one growable device buffer per (device, stream1, stream2), allocated on
+ * the first call on that pair of streams (cudaMalloc) and re-used afterwards.  Calls on the same
+ * streams are ordered by them and share the buffer; calls on other streams get buffers of
  * their own and may overlap on the GPU, as with the reference.  Callers that must not
  * allocate at call time pass their own workspace to rode_spmm_f32 / rode_spmm_f64.
  */

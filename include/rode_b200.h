@@ -133,9 +133,14 @@ int rode_preprocess_cpu(int seg_len, int k_block, int vec_len, int M, const int 
  * is the same, and on graphs with many empty rows those stores were half of the residue
  * kernel's DRAM writes.)
  *
- * Rows split over several segments are summed through `workspace`
- * (rode_spmm_workspace_bytes(m1, n, sizeof(T)) bytes, 16-byte aligned, may be null when
- * that size is 0).  Column byte offsets are formed in 64 bits.
+ * `workspace`: rode_spmm_workspace_bytes(m1, n, sizeof(T)) bytes, 16-byte aligned, contents
+ * don't-care before and after the call.  It holds one partial row per block segment (rows
+ * split over several segments are summed through it, in a fixed order) and, in its last 256
+ * bytes, the counters from which the warps of the large-grid kernels claim their next
+ * segment or bundle of rows (those kernels run as one resident wave of CTAs; the library
+ * zeroes the counters on the call's streams).  With m1 == 0 the workspace may be null; the
+ * residue kernel then runs one CTA per bundle of rows.  Calls that may overlap in time on the
+ * GPU must not share a workspace.  Column byte offsets are formed in 64 bits.
  *
  * The metadata must come from the preprocessing with k_block = 32 and vec_len = 4 (any
  * seg_len that is a multiple of 32), the values the reference's kernels are written for

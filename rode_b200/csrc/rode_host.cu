@@ -27,16 +27,18 @@ int fail(int status, const char *fmt, ...) {
 namespace {
 
 // Scratch buffers owned by the library for callers of the reference-signature entry points,
-// which carry no workspace argument.  One growable buffer per (purpose, device, stream): calls
-// on the same stream are ordered by the stream, so they may share a buffer; calls on different
-// streams may overlap on the GPU and get buffers of their own, which keeps the entry points
-// re-entrant like the reference's.  At most kMaxScratch buffers are kept; the least recently
+// which carry no workspace argument.  One growable buffer per (purpose, device, stream pair):
+// calls on the same streams are ordered by them, so they may share a buffer (the SpMM workspace
+// is used by the block kernel on stream1 and, for its claim counters, by the residue kernel on
+// stream2, hence both streams are part of the key); calls on other streams may overlap on the GPU
+// and get buffers of their own, which keeps the entry points re-entrant like the reference's.  At most kMaxScratch buffers are kept; the least recently
 // used one is released when a new key arrives.  Growing or releasing calls cudaFree, which
 // waits for work that may still use the buffer.
 struct Scratch {
     int kind = 0;
     int dev = -1;
     cudaStream_t stream = nullptr;
+    cudaStream_t stream2 = nullptr;
     void *ptr = nullptr;
     size_t bytes = 0;
     unsigned long long last_use = 0;
@@ -47,7 +49,7 @@ Scratch g_scratch[kMaxScratch];
 unsigned long long g_scratch_clock = 0;
 std::mutex g_scratch_mutex;
 
-int scratch_for(ScratchKind kind, cudaStream_t stream, size_t bytes, void **out) {
+int scratch_for(ScratchKind kind, cudaStream_t stream, cudaStream_t stream2, size_t bytes, void **out) {
     *out = nullptr;
     if (bytes == 0) return RODE_OK;
     int dev = 0;
@@ -55,7 +57,7 @@ int scratch_for(ScratchKind kind, cudaStream_t stream, size_t bytes, void **out)
     std::lock_guard<std::mutex> lock(g_scratch_mutex);
     Scratch *slot = nullptr, *oldest = &g_scratch[0];
     for (Scratch &s : g_scratch) {
-        if (s.ptr && s.kind == kind && s.dev == dev && s.stream == stream) {
+        if (s.ptr && s.kind == kind && s.dev == dev && s.stream == stream && s.stream2 == stream2) {
             slot = &s;
             break;
         }
@@ -76,6 +78,7 @@ int scratch_for(ScratchKind kind, cudaStream_t stream, size_t bytes, void **out)
         slot->kind = kind;
         slot->dev = dev;
         slot->stream = stream;
+        slot->stream2 = stream2;
     }
     if (slot->bytes < bytes) {
         if (slot->ptr) RODE_CUDA_TRY(cudaFree(slot->ptr));
@@ -101,7 +104,7 @@ void spmm_entry(int tile, int m1, int m2, int k, int n, const T *values, const i
     size_t need = 0;
     if (rode_spmm_workspace_bytes(m1, n, static_cast<int>(sizeof(T)), &need) != RODE_OK) return;
     void *ws = nullptr;
-    if (scratch_for(kSpmmScratch, s1, need, &ws) != RODE_OK) return;
+    if (scratch_for(kSpmmScratch, s1, s2, need, &ws) != RODE_OK) return;
     if (sizeof(T) == 4)
         rode_spmm_f32(m1, m2, k, n, reinterpret_cast<const float *>(values), col, row_offsets, blk, res, st,
                       reinterpret_cast<const float *>(B), reinterpret_cast<float *>(C), ws, need, s1, s2);
@@ -201,7 +204,7 @@ void RoDe_preprocess(int N_SEG, int blockX, int vecLen, int M, const int *row_pt
     size_t need = 0;
     if (rode_preprocess_workspace_bytes(M, &need) != RODE_OK) return;
     void *ws = nullptr;
-    if (rode::scratch_for(rode::kPreprocessScratch, nullptr, need, &ws) != RODE_OK) return;
+    if (rode::scratch_for(rode::kPreprocessScratch, nullptr, nullptr, need, &ws) != RODE_OK) return;
     rode::preprocess_reference_signature(N_SEG, blockX, vecLen, M, row_ptr, block_r_ind, st_off, residue_r_ind, n_blk,
                                          n_res, ws);
 }

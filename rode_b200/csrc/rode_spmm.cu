@@ -96,6 +96,18 @@ constexpr int kSmallGridWarps = RODE_SPMM_WIDE_ROWS_CTA_WARPS;  // rows (warps) 
 #ifndef RODE_SPMM_PAIRS_IN_SMEM
 #define RODE_SPMM_PAIRS_IN_SMEM 1
 #endif
+// Claim counters of the persistent block kernel: one int per column tile, at the end of the workspace.
+constexpr size_t kCounterBytes = 256;
+constexpr unsigned kMaxCounterTiles = kCounterBytes / sizeof(int);
+// Residue-row kernel of the 512-byte tile as a persistent grid too (1) or one CTA per bundle of rows (0).
+#ifndef RODE_SPMM_PERSISTENT_ROWS
+#define RODE_SPMM_PERSISTENT_ROWS 1
+#endif
+// Block kernel as a persistent grid: CTAs per SM of the one wave that is launched (0 = one CTA per
+// segment instead).
+#ifndef RODE_SPMM_PERSISTENT_CTAS_PER_SM
+#define RODE_SPMM_PERSISTENT_CTAS_PER_SM 32
+#endif
 // 16-byte units a lane keeps in flight per batch (dense rows per batch = this * 16 / bytes per load / VPL).
 constexpr int kLoadsInFlight = 8;
 
@@ -108,12 +120,12 @@ constexpr int kLoadsInFlight = 8;
 // lane: 8 -> 32 CTAs (64 registers), 12 -> 25 (80), 16 -> 20 (96), more -> no limit.
 constexpr int min_ctas_per_sm(int loads) { return loads <= 8 ? 32 : loads <= 12 ? 25 : loads <= 16 ? 20 : 1; }
 
-template <typename T, int VB, int L, int VPL, int U, int W, bool kHints>
+template <typename T, int VB, int L, int VPL, int U, int W, bool kHints, bool kClaim>
 __global__ void __launch_bounds__(32 * W, min_ctas_per_sm(U * VPL * VB / 16) / W)
 spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
            const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
            const int *__restrict__ st_off, const T *__restrict__ B, T *__restrict__ C, T *__restrict__ partial,
-           const unsigned *__restrict__ hot, int hot_flag_word) {
+           const unsigned *__restrict__ hot, int hot_flag_word, int *__restrict__ next_segment) {
     using V = typename VecB<T, VB>::type;
     constexpr int kLen = VecB<T, VB>::kLen;
     constexpr int G = 32 / L;             // lane groups, each takes every G-th nonzero
@@ -125,8 +137,6 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     // several segments; those that find none exit at once, the others wait for this grid to
     // complete before they read the workspace.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int seg = blockIdx.x * W + (threadIdx.x >> 5);
-    if (seg >= m1) return;
     const int lane = threadIdx.x & 31;
     const int g = lane / L, l = lane % L;
     // Chunk staging (two buffers, so one __syncwarp per chunk orders both the reads after the
@@ -138,7 +148,25 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     const int warp_in_cta = kStage ? (threadIdx.x >> 5) : 0;
     const int stage_slot = (lane % G) * kSteps + lane / G;
     int stage_buf = 0;
+    const size_t row_vecs = static_cast<size_t>(n) / kLen;
+    const size_t col_vec = static_cast<size_t>(blockIdx.y) * L * VPL + l;  // + v * L for vector v
+    const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
+    GatherPolicy policy = {};
+    // the word after the bitmap is the library's verdict on this matrix (0: marks would not help)
+    if constexpr (kHints) policy = make_gather_policy(__ldg(hot + hot_flag_word) != 0u);
 
+    // Persistent form (next_segment != null, a grid of one resident wave): a warp starts with the
+    // segment of its own index and then claims further ones from a counter per column tile, so no
+    // warp slot waits for a new CTA to be launched into it (one-warp CTAs of a few microseconds
+    // each left a fifth of the slots empty at any time).  The claim is issued before the segment's
+    // work and read after it, so its latency is hidden.  Otherwise one segment per warp.
+    int seg = blockIdx.x * W + (threadIdx.x >> 5);
+    while (seg < m1) {
+    int claimed = INT_MAX;
+    if constexpr (kClaim) {
+        if (next_segment != nullptr && lane == 0)
+            claimed = static_cast<int>(gridDim.x) * W + atomicAdd(next_segment + blockIdx.y, 1);
+    }
     const int row = __ldg(block_r_ind + seg);
     const int off = __ldg(st_off + seg);
     const int next = (seg + 1 < m1) ? __ldg(st_off + seg + 1) : INT_MAX;
@@ -146,10 +174,6 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     const int row_end = __ldg(row_offsets + row + 1);
     const int end = min(row_end, next);
     const bool whole_row = (off == row_begin) && (next >= row_end);
-
-    const size_t row_vecs = static_cast<size_t>(n) / kLen;
-    const size_t col_vec = static_cast<size_t>(blockIdx.y) * L * VPL + l;  // + v * L for vector v
-    const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
 
     // (column, value) of this lane's nonzero in the current and in the next chunk
     int c_cur = 0, c_nxt = 0;
@@ -165,12 +189,7 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     // With popularity hints a column index carries its mark in bit 31.  The bitmap word of a
     // column is fetched one chunk after the column itself (which has arrived by then) and one
     // chunk before the column is used, so the lookup adds no exposed latency after the first.
-    GatherPolicy policy = {};
-    if constexpr (kHints) {
-        // the word after the bitmap is the library's verdict on this matrix (0: marks would not help)
-        policy = make_gather_policy(__ldg(hot + hot_flag_word) != 0u);
-        c_cur = tag_hot(c_cur, hot_word(hot, c_cur));
-    }
+    if constexpr (kHints) c_cur = tag_hot(c_cur, hot_word(hot, c_cur));
 
     V acc[VPL];
 #pragma unroll
@@ -238,6 +257,8 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
                 reinterpret_cast<V *>(partial)[static_cast<size_t>(seg) * row_vecs + col_vec + v * L] = acc[v];
         }
     }
+    seg = kClaim ? __shfl_sync(kFull, claimed, 0) : INT_MAX;
+    }  // segments of this warp
 }
 
 // ---------------------------------------------------------------------------------------
@@ -337,20 +358,38 @@ template <typename T, int L>
 __global__ void __launch_bounds__(kCtaThreads, (sizeof(T) == 4 ? 32 : 16) / kCtaWarps)  // fp32: 64 registers
 spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
           const int *__restrict__ column_indices, const int *__restrict__ row_offsets,
-          const int *__restrict__ residue_r_ind, const T *__restrict__ B, T *__restrict__ C) {
+          const int *__restrict__ residue_r_ind, const T *__restrict__ B, T *__restrict__ C,
+          int *__restrict__ next_group) {
     using V = typename Vec16<T>::type;
     constexpr int kLen = Vec16<T>::kLen;
     constexpr int U = (kLoadsInFlight < L) ? kLoadsInFlight : L;  // rows per batch
     constexpr int NB = (L + U - 1) / U;  // batches per L-nonzero chunk
     constexpr int kAlign = 4;            // vec_len of the preprocessing
     constexpr int kBlockK = 32;          // k_block of the preprocessing
-    const long long group = (static_cast<long long>(blockIdx.x) * kCtaThreads + threadIdx.x) / L;
-    if (group * rows_per_group >= m2) return;  // the whole group leaves
-    const int item0 = static_cast<int>(group * rows_per_group);
     const int lane = threadIdx.x & 31;
     const int l = lane % L;
     const unsigned gmask = group_mask<L>(lane);
     const int gshift = lane & ~(L - 1);
+    // chunk staging in shared memory as in spmm_block (one region of L pairs per lane group)
+    constexpr bool kStage = RODE_SPMM_PAIRS_IN_SMEM != 0 && (L % U == 0) && (U % 4 == 0);
+    __shared__ __align__(16) int s_col[2][kStage ? kCtaThreads : 1];
+    __shared__ __align__(16) T s_val[2][kStage ? kCtaThreads : 1];
+    const int stage_base = (threadIdx.x / L) * L;  // first slot of this group's region
+    int stage_buf = 0;
+    // Persistent form (next_group != null, a grid of one resident wave): a lane group starts with
+    // the bundle of rows of its own index and claims further bundles from a counter per column
+    // tile; the claim is issued before the bundle's work and read after it.
+    const long long n_groups = (static_cast<long long>(m2) + rows_per_group - 1) / rows_per_group;
+    long long group = (static_cast<long long>(blockIdx.x) * kCtaThreads + threadIdx.x) / L;
+    while (group < n_groups) {
+    int claimed = INT_MAX;
+    constexpr bool kClaim = sizeof(T) == 4;  // fp64: 12 more registers for it cost more than it gains
+    if constexpr (kClaim) {
+        if (next_group != nullptr && l == 0)
+            claimed = static_cast<int>(gridDim.x) * (kCtaThreads / L) + atomicAdd(next_group + blockIdx.y, 1);
+    }
+    [&]() {
+    const int item0 = static_cast<int>(group * rows_per_group);
 
     // ---- descriptors: lane j of the group owns residue row item0 + j -----------------------
     int row = 0, begin = 0, len = 0;
@@ -411,13 +450,6 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
     int pos = 0;
     V acc = vzero(static_cast<V *>(nullptr));
 
-    // chunk staging in shared memory as in spmm_block (one region of L pairs per lane group)
-    constexpr bool kStage = RODE_SPMM_PAIRS_IN_SMEM != 0 && (L % U == 0) && (U % 4 == 0);
-    __shared__ __align__(16) int s_col[2][kStage ? kCtaThreads : 1];
-    __shared__ __align__(16) T s_val[2][kStage ? kCtaThreads : 1];
-    const int stage_base = (threadIdx.x / L) * L;  // first slot of this group's region
-    int stage_buf = 0;
-
     for (int base = 0; base < total; base += L) {
         const int cnt = min(L, total - base);
         int c_pre;
@@ -472,6 +504,9 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
         v_nxt = v_pre;
         stage_buf ^= 1;
     }
+    }();
+    group = kClaim ? __shfl_sync(gmask, claimed, 0, L) : n_groups;
+    }  // bundles of this group
 }
 
 // ---------------------------------------------------------------------------------------
@@ -659,14 +694,14 @@ spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restric
 
 template <typename T, int VB, int L, int VPL>
 int launch_rows(int m2, int n, const T *values, const int *col, const int *row_offsets, const int *residue_r_ind,
-                const T *B, T *C, cudaStream_t s2);
+                const T *B, T *C, int *counters, cudaStream_t s2);
 
 // Block kernel of shape (VB bytes per load, L lanes, VPL loads per lane) and residue-row kernel
 // of shape (RVB, RL, RVPL); both cover the same column tile.
 template <typename T, int VB, int L, int VPL, int RVB, int RL, int RVPL>
 int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, const int *row_offsets,
                  const int *block_r_ind, const int *residue_r_ind, const int *st_off, const T *B, T *C,
-                 T *partial, const unsigned *hot, cudaStream_t s1, cudaStream_t s2) {
+                 T *partial, int *counters, const unsigned *hot, cudaStream_t s1, cudaStream_t s2) {
     static_assert(L * VPL * VB == RL * RVPL * RVB, "block and residue kernels must cover the same tile");
     constexpr int kTileWidth = L * VPL * VecB<T, VB>::kLen;
     constexpr int U = kLoadsInFlight * 16 / VB / VPL;            // rows per batch, large grids
@@ -680,25 +715,38 @@ int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, 
         // (segments of 32 to 512 nonzeros side by side) ran 0.035 ms instead of 0.029 ms at
         // N = 32 and 0.27 ms instead of 0.06 ms at N = 128.
         const bool small_grid = static_cast<long long>(m1) * tiles <= 2LL * 32 * sm_count();
-        dim3 grid((m1 + kCtaWarps - 1) / kCtaWarps, tiles);
+        // large grids: one resident wave of CTAs whose warps claim segments from counters (one per
+        // column tile) at the end of the workspace, zeroed on the stream before the launch
+        const int ctas_needed = (m1 + kCtaWarps - 1) / kCtaWarps;
+        const int resident = RODE_SPMM_PERSISTENT_CTAS_PER_SM * sm_count();
+        // (fp32 only: the fp64 kernels, bound by DRAM on twice the bytes, measured 5 % slower with it)
+        const bool persistent = RODE_SPMM_PERSISTENT_CTAS_PER_SM > 0 && sizeof(T) == 4 && !small_grid &&
+                                counters != nullptr &&
+                                tiles <= kMaxCounterTiles / 2 && ctas_needed > 2 * (resident / static_cast<int>(tiles));
+        int *claim = nullptr;
+        if (persistent) {
+            RODE_CUDA_TRY(cudaMemsetAsync(counters, 0, sizeof(int) * tiles, s1));
+            claim = counters;
+        }
+        dim3 grid(persistent ? (resident + tiles - 1) / tiles : ctas_needed, tiles);
         bool launched = false;
         // Popularity hints: block kernel of the 512-byte tile only.  In the residue-row kernel
         // the marks saved DRAM bytes (5.36 -> 4.79 GB on R-MAT scale 23) but the extra registers
         // cost more time than that returned (1.41 -> 1.52 ms).
         if constexpr (L * VPL * VB == 512) {
             if (hot && !small_grid) {
-                spmm_block<T, VB, L, VPL, U, kCtaWarps, true><<<grid, kCtaThreads, 0, s1>>>(
-                    m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, hot, (k + 31) / 32);
+                spmm_block<T, VB, L, VPL, U, kCtaWarps, true, true><<<grid, kCtaThreads, 0, s1>>>(
+                    m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, hot, (k + 31) / 32, claim);
                 launched = true;
             }
         }
         if (launched) {
         } else if (small_grid && USmall > U) {
-            spmm_block<T, VB, L, VPL, USmall, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
-                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0);
+            spmm_block<T, VB, L, VPL, USmall, kCtaWarps, false, false><<<grid, kCtaThreads, 0, s1>>>(
+                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0, claim);
         } else {
-            spmm_block<T, VB, L, VPL, U, kCtaWarps, false><<<grid, kCtaThreads, 0, s1>>>(
-                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0);
+            spmm_block<T, VB, L, VPL, U, kCtaWarps, false, true><<<grid, kCtaThreads, 0, s1>>>(
+                m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0, claim);
         }
         RODE_CHECK_LAUNCH("rode::spmm_block");
         // fix-up as a programmatic dependent of spmm_block: its launch latency and its
@@ -718,13 +766,14 @@ int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, 
                                          C));
         RODE_CHECK_LAUNCH("rode::spmm_fixup");
     }
-    if (m2 > 0) return launch_rows<T, RVB, RL, RVPL>(m2, n, values, col, row_offsets, residue_r_ind, B, C, s2);
+    if (m2 > 0)
+        return launch_rows<T, RVB, RL, RVPL>(m2, n, values, col, row_offsets, residue_r_ind, B, C, counters, s2);
     return RODE_OK;
 }
 
 template <typename T, int VB, int L, int VPL>
 int launch_rows(int m2, int n, const T *values, const int *col, const int *row_offsets, const int *residue_r_ind,
-                const T *B, T *C, cudaStream_t s2) {
+                const T *B, T *C, int *counters, cudaStream_t s2) {
     constexpr int kTileWidth = L * VPL * VecB<T, VB>::kLen;
     const unsigned tiles = static_cast<unsigned>(n / kTileWidth);
     {
@@ -736,9 +785,19 @@ int launch_rows(int m2, int n, const T *values, const int *col, const int *row_o
             per_group = per_group < 4 ? 4 : (per_group > 32 ? 32 : per_group);
             const long long groups = (static_cast<long long>(m2) + per_group - 1) / per_group;
             constexpr int kGroupsPerCta = kCtaThreads / 32;
-            dim3 grid(static_cast<unsigned>((groups + kGroupsPerCta - 1) / kGroupsPerCta), tiles);
+            const long long ctas_needed = (groups + kGroupsPerCta - 1) / kGroupsPerCta;
+            const long long resident = static_cast<long long>(RODE_SPMM_PERSISTENT_CTAS_PER_SM) * sm_count();
+            const bool persistent = RODE_SPMM_PERSISTENT_ROWS != 0 && sizeof(T) == 4 && counters != nullptr &&
+                                    tiles <= kMaxCounterTiles / 2 &&
+                                    ctas_needed > 2 * (resident / tiles);
+            int *claim = nullptr;
+            if (persistent) {
+                claim = counters + kMaxCounterTiles / 2;  // second half: the residue kernel's counters
+                RODE_CUDA_TRY(cudaMemsetAsync(claim, 0, sizeof(int) * tiles, s2));
+            }
+            dim3 grid(static_cast<unsigned>(persistent ? (resident + tiles - 1) / tiles : ctas_needed), tiles);
             spmm_rows<T, 32><<<grid, kCtaThreads, 0, s2>>>(m2, per_group, n, values, col, row_offsets,
-                                                           residue_r_ind, B, C);
+                                                           residue_r_ind, B, C, claim);
         } else if (static_cast<long long>(m2) * tiles <= RODE_SPMM_WIDE_ROWS_WAVES * 32LL * sm_count()) {
             dim3 grid((m2 + kSmallGridWarps - 1) / kSmallGridWarps, tiles);
             spmm_rows_wide<T, VB, L, VPL><<<grid, 32 * kSmallGridWarps, 0, s2>>>(m2, n, values, col, row_offsets,
@@ -780,25 +839,30 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
         return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: n = %d exceeds the supported width (%d)", n, 65535 * 8 * kLen);
     size_t need = 0;
     rode_spmm_workspace_bytes(m1, n, static_cast<int>(sizeof(T)), &need);
-    if (need > 0) {
+    // Without block segments the workspace holds the claim counters only and may be left out (the
+    // residue kernel then runs one CTA per bundle of rows).
+    if (m1 > 0 || workspace != nullptr) {
         if (workspace == nullptr || workspace_bytes < need)
             return fail(RODE_ERR_WORKSPACE, "spmm: workspace of %zu bytes needed, %zu given", need,
                         workspace ? workspace_bytes : static_cast<size_t>(0));
         if (!aligned_to(workspace, 16)) return fail(RODE_ERR_WORKSPACE, "spmm: workspace must be 16-byte aligned");
     }
     T *partial = static_cast<T *>(workspace);
+    // the claim counters of the persistent block kernel sit behind the partial rows
+    int *counters = workspace != nullptr
+                        ? reinterpret_cast<int *>(static_cast<char *>(workspace) + need - kCounterBytes) : nullptr;
     // Widest tile (32, 16 or 8 vectors of 16 bytes) that divides the row.  Shapes are given in
     // 16-byte vectors; with 32-byte loads (operands 32-byte aligned) a group has half the lanes.
     // The batched residue kernel of the widest tile (shape 3201) always loads 16 bytes per lane.
 #define RODE_LAUNCH16(shape, rows_shape)                                                                        \
     launch_shape<T, 16, (shape) / 100, (shape) % 100, 16, (rows_shape) / 100, (rows_shape) % 100>(              \
-        m1, m2, k, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, hot, stream1, \
+        m1, m2, k, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, counters, hot, stream1, \
         stream2)
 #define RODE_LAUNCH32(shape, rows_shape, rows_bytes)                                                             \
     launch_shape<T, 32, wide_lanes(shape), wide_vpl(shape), rows_bytes,                                          \
                  (rows_bytes) == 32 ? wide_lanes(rows_shape) : (rows_shape) / 100,                               \
                  (rows_bytes) == 32 ? wide_vpl(rows_shape) : (rows_shape) % 100>(                                \
-        m1, m2, k, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, hot, stream1, \
+        m1, m2, k, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, counters, hot, stream1, \
         stream2)
     const int vecs = n / kLen;
     // 32-byte loads measured no faster than 16-byte ones on any benchmark matrix (the gathers are
@@ -831,7 +895,9 @@ extern "C" {
 int rode_spmm_workspace_bytes(int m1, int n, int elem_size, size_t *bytes) {
     if (bytes == nullptr || m1 < 0 || n < 0 || (elem_size != 4 && elem_size != 8))
         return rode::fail(RODE_ERR_INVALID_ARGUMENT, "spmm_workspace_bytes: bad argument");
-    *bytes = static_cast<size_t>(m1) * static_cast<size_t>(n) * static_cast<size_t>(elem_size);
+    // one partial row per block segment, rounded up to 256 bytes, then the claim counters
+    const size_t rows = static_cast<size_t>(m1) * static_cast<size_t>(n) * static_cast<size_t>(elem_size);
+    *bytes = (rows + 255) / 256 * 256 + rode::kCounterBytes;
     return RODE_OK;
 }
 

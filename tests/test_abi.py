@@ -44,8 +44,10 @@ def test_version_and_sizes(built_library):
     assert capi.preprocess_workspace_bytes(0) == 8
     assert capi.preprocess_workspace_bytes(1024) == 8
     assert capi.preprocess_workspace_bytes(1025) == 16
-    assert capi.spmm_workspace_bytes(10, 128, 4) == 10 * 128 * 4
-    assert capi.spmm_workspace_bytes(0, 128, 8) == 0
+    # one partial row per block segment, rounded up to 256 bytes, plus 256 bytes of claim counters
+    assert capi.spmm_workspace_bytes(10, 128, 4) == 10 * 128 * 4 + 256
+    assert capi.spmm_workspace_bytes(3, 32, 4) == 512 + 256
+    assert capi.spmm_workspace_bytes(0, 128, 8) == 256
     assert capi.preprocess_capacity(512, 4, 100, 5000) == (5000 + 300) // 512 + 100
 
 
