@@ -48,6 +48,8 @@ enum ScratchKind { kSpmmScratch = 0, kPreprocessScratch = 1 };
 Scratch g_scratch[kMaxScratch];
 unsigned long long g_scratch_clock = 0;
 std::mutex g_scratch_mutex;
+// Held from the look-up of a library-owned buffer until the kernels that use it are enqueued.
+std::mutex g_enqueue_mutex;
 
 int scratch_for(ScratchKind kind, cudaStream_t stream, cudaStream_t stream2, size_t bytes, void **out) {
     *out = nullptr;
@@ -103,6 +105,9 @@ void spmm_entry(int tile, int m1, int m2, int k, int n, const T *values, const i
     }
     size_t need = 0;
     if (rode_spmm_workspace_bytes(m1, n, static_cast<int>(sizeof(T)), &need) != RODE_OK) return;
+    // Looking the buffer up and enqueueing the kernels that use it is one step: two host threads
+    // that call on the same streams must not interleave their launches on the shared buffer.
+    std::lock_guard<std::mutex> enqueue(g_enqueue_mutex);
     void *ws = nullptr;
     if (scratch_for(kSpmmScratch, s1, s2, need, &ws) != RODE_OK) return;
     if (sizeof(T) == 4)
@@ -203,6 +208,7 @@ void RoDe_preprocess(int N_SEG, int blockX, int vecLen, int M, const int *row_pt
                      int *residue_r_ind, int *n_blk, int *n_res) {
     size_t need = 0;
     if (rode_preprocess_workspace_bytes(M, &need) != RODE_OK) return;
+    std::lock_guard<std::mutex> enqueue(rode::g_enqueue_mutex);
     void *ws = nullptr;
     if (rode::scratch_for(rode::kPreprocessScratch, nullptr, nullptr, need, &ws) != RODE_OK) return;
     rode::preprocess_reference_signature(N_SEG, blockX, vecLen, M, row_ptr, block_r_ind, st_off, residue_r_ind, n_blk,

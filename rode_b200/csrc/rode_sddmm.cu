@@ -40,6 +40,7 @@
 // Per nonzero: 12 B of CSR data/output plus 4*K bytes of rhs (L1/L2/HBM by reuse); per item
 // 4*K bytes of lhs per group that touches it.  No atomics, no workspace in global memory.
 #include <climits>
+#include <mutex>
 
 #include "rode_common.cuh"
 
@@ -423,23 +424,32 @@ sddmm_items(int n_items, int items_per_warp, const int *__restrict__ item_rows, 
 // One warp per block segment (used where segments are long, K = 32 and 64: up to 543
 // nonzeros): coalesced chunk loads without any search, the G groups take consecutive
 // L-nonzero pieces of each 32-nonzero chunk, the lhs slice stays in registers.
-template <int L, int VPL>
+//
+// kClaim (grids of one resident wave): a warp starts with the segment of its own index and
+// claims further ones from *next_segment; the claim is issued before the segment's work and
+// read after it.  One-warp CTAs of one segment each live a few microseconds, and a fifth of the
+// warp slots stood empty waiting for the next CTA to be launched into them.
+template <int L, int VPL, bool kClaim>
 __global__ void __launch_bounds__(32, 32)  // 64 registers: 32 one-warp CTAs per SM
 sddmm_block(int m1, const int *__restrict__ block_r_ind, const int *__restrict__ st_off,
             const int *__restrict__ row_offsets, const int *__restrict__ column_indices,
             const float *__restrict__ values, const float *__restrict__ lhs, const float *__restrict__ rhs,
-            float *__restrict__ out) {
+            float *__restrict__ out, int *__restrict__ next_segment) {
     constexpr int kBatch = kLoadsInFlight / VPL;
     constexpr size_t kRowVecs = L * VPL;
     constexpr bool kStage = RODE_SDDMM_COLUMNS_IN_SMEM != 0 && (kBatch % 4 == 0);
     __shared__ __align__(16) int s_col[2][32];  // column indices of the current chunk, two buffers
     int stage_buf = 0;
-    const int seg = blockIdx.x;
-    if (seg >= m1) return;
     const int lane = threadIdx.x;
     const int l = lane % L;
     const int gbase = lane - l;  // first lane (= first nonzero of the chunk) of this group
     const unsigned gmask = group_mask<L>(lane);
+    int seg = blockIdx.x;
+    while (seg < m1) {
+    int claimed = INT_MAX;  // never used in arithmetic: the loop test compares it with m1 as it is
+    if constexpr (kClaim) {
+        if (lane == 0) claimed = static_cast<int>(gridDim.x) + atomicAdd(next_segment, 1);
+    }
 
     const int row = __ldg(block_r_ind + seg);
     const int off = __ldg(st_off + seg);
@@ -512,6 +522,54 @@ sddmm_block(int m1, const int *__restrict__ block_r_ind, const int *__restrict__
         v_nxt = v_pre;
         stage_buf ^= 1;
     }
+    seg = kClaim ? __shfl_sync(kFull, claimed, 0) : INT_MAX;
+    }  // segments of this warp
+}
+
+// ---------------------------------------------------------------------------------------
+// Claim counter of the persistent block grid.  The SDDMM entry points carry no workspace, so the
+// counters live in a fixed array of the library's device image: kClaimSlots slots of 64 ints
+// (32 KB on every GPU that loads the library).  A slot belongs to one (device, stream1, stream2)
+// for the life of the process: calls on the same streams are ordered by them and may share
+// their counter, calls on other streams get other slots; when all slots are taken a call simply
+// runs one CTA per segment.  Nothing is allocated.  (Two host threads that enqueue calls on the
+// SAME pair of streams at the same time could interleave one call's counter reset with the
+// other's kernel; like the reference, the entry points expect one enqueueing thread per stream.)
+#ifndef RODE_SDDMM_PERSISTENT
+#define RODE_SDDMM_PERSISTENT 1
+#endif
+constexpr int kClaimSlots = 128;
+constexpr int kClaimInts = 64;
+static __device__ __align__(256) int g_claim_counters[kClaimSlots * kClaimInts];
+
+int claim_counters(cudaStream_t s1, cudaStream_t s2, int **out) {
+    struct Key {
+        int dev;
+        cudaStream_t s1, s2;
+    };
+    static Key keys[kClaimSlots];
+    static int n_keys = 0;
+    static int *base[64] = {nullptr};  // device address of the array, per device
+    static std::mutex lock;
+    *out = nullptr;
+    int dev = 0;
+    RODE_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return RODE_OK;
+    std::lock_guard<std::mutex> guard(lock);
+    if (base[dev] == nullptr) {
+        void *p = nullptr;
+        RODE_CUDA_TRY(cudaGetSymbolAddress(&p, g_claim_counters));
+        base[dev] = static_cast<int *>(p);
+    }
+    int slot = -1;
+    for (int i = 0; i < n_keys; ++i)
+        if (keys[i].dev == dev && keys[i].s1 == s1 && keys[i].s2 == s2) slot = i;
+    if (slot < 0 && n_keys < kClaimSlots) {
+        slot = n_keys++;
+        keys[slot] = {dev, s1, s2};
+    }
+    if (slot >= 0) *out = base[dev] + slot * kClaimInts;
+    return RODE_OK;
 }
 
 // Items per warp: 32 when that still gives every SM several waves of warps, fewer otherwise.
@@ -528,7 +586,19 @@ int launch_k(int m1, int m2, int seg_cap, const int *block_r_ind, const int *res
              float *out, cudaStream_t s1, cudaStream_t s2) {
     if (m1 > 0) {
         if (seg_cap < 32 && RODE_SDDMM_LONG_SEGMENTS_BY_WARP) {
-            sddmm_block<L, VPL><<<m1, 32, 0, s1>>>(m1, block_r_ind, st_off, row_offsets, col, values, lhs, rhs, out);
+            const int resident = 32 * sm_count();
+            int *claim = nullptr;
+            if (RODE_SDDMM_PERSISTENT && m1 > 2 * resident) {
+                if (int rc = claim_counters(s1, s2, &claim)) return rc;
+            }
+            if (claim != nullptr) {
+                RODE_CUDA_TRY(cudaMemsetAsync(claim, 0, sizeof(int), s1));
+                sddmm_block<L, VPL, true><<<resident, 32, 0, s1>>>(m1, block_r_ind, st_off, row_offsets, col, values, lhs,
+                                                                   rhs, out, claim);
+            } else {
+                sddmm_block<L, VPL, false><<<m1, 32, 0, s1>>>(m1, block_r_ind, st_off, row_offsets, col, values, lhs, rhs,
+                                                              out, nullptr);
+            }
             RODE_CHECK_LAUNCH("rode::sddmm_block");
         } else {
             const int per = items_per_warp(m1, seg_cap);
