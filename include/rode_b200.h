@@ -206,8 +206,13 @@ int rode_spmm_f64_hot(int m1, int m2, int k, int n, const double *values, const 
  * lhs is [M x k], rhs is [n x k], both row-major; out is fp32[nnz] aligned with values.
  * Block segments run on stream1, pure-residue rows on stream2.  A null stream is the
  * default stream (the reference silently skips a kernel whose stream handle is null,
- * RoDeSddmm.cu:503,509; this library does not).  Needs no workspace.  Metadata as for SpMM:
- * k_block = 32, vec_len = 4, any seg_len that is a multiple of 32.
+ * RoDeSddmm.cu:503,509; this library does not).  Needs no workspace: the one counter the
+ * large-grid block kernel claims its segments from lives in a fixed array of the library's
+ * device image (32 KB per GPU), one slot per (device, stream1, stream2) seen by the process;
+ * calls on the same streams are ordered by them, calls on other streams use other slots, and
+ * beyond 128 distinct stream pairs the kernel runs one CTA per segment instead.  As with the
+ * reference, one host thread at a time should enqueue calls on a given pair of streams.
+ * Metadata as for SpMM: k_block = 32, vec_len = 4, any seg_len that is a multiple of 32.
  */
 int rode_sddmm_f32(int m1, int m2, int n, int k, const int *block_r_ind, const int *residue_r_ind,
                    const int *st_off, const int *row_offsets, const int *column_indices,

@@ -209,3 +209,27 @@ def test_sddmm_row_mode_every_entry(oracle_cpu, k):
     out = capi.sddmm(meta, d.row_ptr, d.col, d.val, lhs.cuda(), rhs.cuda(), out=out0)
     torch.cuda.synchronize()
     _check(oracle_cpu, A, lhs, rhs, out, f"row mode k={k}")
+
+
+def test_sddmm_calls_on_different_stream_pairs_run_side_by_side():
+    """Large block grids run as one resident wave whose warps claim segments from a counter that
+    the library keeps per pair of streams: two calls on different pairs, in flight together,
+    must not disturb each other, and repeated calls on one pair reuse its counter."""
+    A = W.pareto_rows(m=400_000, n=400_000, cap=60_000, device="cuda", seed=21)
+    meta = capi.preprocess(A.row_ptr, A.nnz, 512, 32, 4)
+    assert meta.m1 > 2 * 32 * 148          # more than two waves of one-warp CTAs
+    k = 64
+    lhs, rhs = W.dense(A.m, k, device="cuda", seed=5), W.dense(A.n, k, device="cuda", seed=6)
+    want = capi.sddmm(meta, A.row_ptr, A.col, A.val, lhs, rhs)
+    torch.cuda.synchronize()
+    pairs = [(torch.cuda.Stream(), torch.cuda.Stream()) for _ in range(3)]
+    outs = [torch.full((A.nnz,), float("nan"), device="cuda") for _ in pairs]
+    for _ in range(2):                       # second round: every pair uses its counter again
+        for (s1, s2), out in zip(pairs, outs):
+            out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        for (s1, s2), out in zip(pairs, outs):
+            capi.sddmm(meta, A.row_ptr, A.col, A.val, lhs, rhs, out=out, stream1=s1, stream2=s2)
+        torch.cuda.synchronize()
+        for out in outs:
+            assert torch.equal(out, want)
