@@ -287,6 +287,12 @@ def spmm(meta: RodeMeta, row_ptr: torch.Tensor, col: torch.Tensor, values: torch
         need = spmm_workspace_bytes(meta.m1, n, B.element_size())
         if workspace is None and need:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+            # the buffer goes back to torch's allocator when this function returns: tell the
+            # allocator which other streams still use it, or a call enqueued right afterwards
+            # could be handed the same memory while this call's kernels run
+            for s in (s1, s2):
+                if isinstance(s, torch.cuda.Stream) and s != cur:
+                    workspace.record_stream(s)
         ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
         spmm_raw(B.dtype, meta.m1, meta.m2, k, n, values.data_ptr(), col.data_ptr(), row_ptr.data_ptr(),
                  meta.block_r_ind.data_ptr(), meta.residue_r_ind.data_ptr(), meta.st_off.data_ptr(), B.data_ptr(),

@@ -207,8 +207,9 @@ torch::Tensor py_spmm_forward(torch::Tensor block_indices, torch::Tensor residue
                                            dense.data_ptr<double>(), out.data_ptr<double>(), ws.data_ptr(), ws_bytes,
                                            hot, s1, s2));
     });
-    // The workspace is used on the current stream only (block + fix-up kernels); the side
-    // stream was joined back, so the caching allocator may reuse it after this call.
+    // The workspace is used by the block and fix-up kernels on the current stream and, for its
+    // claim counters, by the residue kernel on the side stream; the side stream was joined back
+    // into the current one, so the caching allocator may reuse the buffer after this call.
     return out;
 }
 

@@ -266,3 +266,37 @@ def test_spmm_matches_reference_kernel_fixtures(oracle_cpu, golden_dir):
         C = capi.spmm(meta, d.row_ptr, d.col, d.val, torch.from_numpy(a["B"]).cuda())
         scale = spmm_abs_scale(a["row_ptr"], a["col"], a["val"], a["B"])
         assert_close_to_truth(C.cpu().numpy(), a["C"].astype(np.float64), 2 * scale, case)
+
+
+def test_spmm_persistent_grids_on_stream_pairs_in_flight_together():
+    """Grids of more than two waves run as one resident wave whose warps claim their work from
+    counters at the end of the workspace.  Calls with workspaces of their own (C ABI), and calls
+    through the reference's signature (library-owned workspaces, one per pair of streams), on
+    different stream pairs and in flight together, must all give the result of a lone call."""
+    lib = capi.load()
+    A = W.pareto_rows(m=400_000, n=400_000, cap=60_000, device="cuda", seed=21)
+    meta = capi.preprocess(A.row_ptr, A.nnz)
+    assert meta.m1 > 2 * 32 * 148 and meta.m2 > 2 * 32 * 32 * 148
+    n = 128
+    B = W.dense(A.n, n, device="cuda", seed=3)
+    want = capi.spmm(meta, A.row_ptr, A.col, A.val, B)
+    torch.cuda.synchronize()
+    pairs = [(torch.cuda.Stream(), torch.cuda.Stream()) for _ in range(4)]
+    outs = [torch.zeros((A.m, n), device="cuda") for _ in pairs]
+    fn = getattr(lib, capi.CPP_SYMBOLS["RoDeSpmm_n128_f32"])
+    fn.restype = None
+    vp = ctypes.c_void_p
+    for _ in range(2):                       # second round: buffers and counters are used again
+        for out in outs:
+            out.zero_()
+        torch.cuda.synchronize()
+        for i, ((s1, s2), out) in enumerate(zip(pairs, outs)):
+            if i % 2 == 0:
+                capi.spmm(meta, A.row_ptr, A.col, A.val, B, C=out, stream1=s1, stream2=s2)
+            else:
+                fn(meta.m1, meta.m2, A.n, n, vp(A.val.data_ptr()), vp(A.col.data_ptr()), vp(A.row_ptr.data_ptr()),
+                   vp(meta.block_r_ind.data_ptr()), vp(meta.residue_r_ind.data_ptr()), vp(meta.st_off.data_ptr()),
+                   vp(B.data_ptr()), vp(out.data_ptr()), vp(s1.cuda_stream), vp(s2.cuda_stream))
+        torch.cuda.synchronize()
+        for out in outs:
+            assert torch.equal(out, want)
