@@ -588,7 +588,7 @@ int launch_k(int m1, int m2, int seg_cap, const int *block_r_ind, const int *res
         if (seg_cap < 32 && RODE_SDDMM_LONG_SEGMENTS_BY_WARP) {
             const int resident = 32 * sm_count();
             int *claim = nullptr;
-            if (RODE_SDDMM_PERSISTENT && m1 > 2 * resident) {
+            if (RODE_SDDMM_PERSISTENT && m1 > 16 * resident) {  // from about 16 segments per warp on it pays
                 if (int rc = claim_counters(s1, s2, &claim)) return rc;
             }
             if (claim != nullptr) {

@@ -103,6 +103,10 @@ constexpr unsigned kMaxCounterTiles = kCounterBytes / sizeof(int);
 #ifndef RODE_SPMM_PERSISTENT_ROWS
 #define RODE_SPMM_PERSISTENT_ROWS 1
 #endif
+// A grid becomes persistent from this many resident waves of work on: with fewer segments per warp
+// the claimed order's tail (one long segment claimed last) costs more than the launch gaps it
+// saves (measured: gain from about 20 segments per warp, loss below 10).
+constexpr int kPersistentMinWaves = 16;
 // Block kernel as a persistent grid: CTAs per SM of the one wave that is launched (0 = one CTA per
 // segment instead).
 #ifndef RODE_SPMM_PERSISTENT_CTAS_PER_SM
@@ -722,7 +726,8 @@ int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, 
         // (fp32 only: the fp64 kernels, bound by DRAM on twice the bytes, measured 5 % slower with it)
         const bool persistent = RODE_SPMM_PERSISTENT_CTAS_PER_SM > 0 && sizeof(T) == 4 && !small_grid &&
                                 counters != nullptr &&
-                                tiles <= kMaxCounterTiles / 2 && ctas_needed > 2 * (resident / static_cast<int>(tiles));
+                                tiles <= kMaxCounterTiles / 2 &&
+                                ctas_needed > kPersistentMinWaves * (resident / static_cast<int>(tiles));
         int *claim = nullptr;
         if (persistent) {
             RODE_CUDA_TRY(cudaMemsetAsync(counters, 0, sizeof(int) * tiles, s1));
@@ -789,7 +794,7 @@ int launch_rows(int m2, int n, const T *values, const int *col, const int *row_o
             const long long resident = static_cast<long long>(RODE_SPMM_PERSISTENT_CTAS_PER_SM) * sm_count();
             const bool persistent = RODE_SPMM_PERSISTENT_ROWS != 0 && sizeof(T) == 4 && counters != nullptr &&
                                     tiles <= kMaxCounterTiles / 2 &&
-                                    ctas_needed > 2 * (resident / tiles);
+                                    ctas_needed > kPersistentMinWaves * (resident / tiles);
             int *claim = nullptr;
             if (persistent) {
                 claim = counters + kMaxCounterTiles / 2;  // second half: the residue kernel's counters

@@ -274,9 +274,10 @@ def test_spmm_persistent_grids_on_stream_pairs_in_flight_together():
     through the reference's signature (library-owned workspaces, one per pair of streams), on
     different stream pairs and in flight together, must all give the result of a lone call."""
     lib = capi.load()
-    A = W.pareto_rows(m=400_000, n=400_000, cap=60_000, device="cuda", seed=21)
+    A = W.rmat(scale=22, device="cuda")
     meta = capi.preprocess(A.row_ptr, A.nnz)
-    assert meta.m1 > 2 * 32 * 148 and meta.m2 > 2 * 32 * 32 * 148
+    # enough segments and enough bundles of 32 residue rows for both kernels to run as persistent grids
+    assert meta.m1 > 16 * 32 * 148 and meta.m2 > 16 * 32 * 32 * 148
     n = 128
     B = W.dense(A.n, n, device="cuda", seed=3)
     want = capi.spmm(meta, A.row_ptr, A.col, A.val, B)
