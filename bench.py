@@ -286,6 +286,44 @@ def time_hot_columns(col, n_cols, row_bytes, iters):
             "budget": "60 % of the device's L2"}
 
 
+class NumaBinding:
+    """Context manager: while it is entered the process runs on the CPUs of the NUMA node the
+    given GPU hangs on (read from sysfs), so that host memory allocated and first touched inside
+    lands on that node.  Does nothing where the node cannot be determined."""
+
+    def __init__(self, device):
+        self.cpus, self.node, self.saved = None, None, None
+        try:
+            prop = torch.cuda.get_device_properties(device)
+            bus = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+            with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+                node = int(f.read().strip())
+            if node < 0:
+                return
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+                cpus = set()
+                for part in f.read().strip().split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            allowed = os.sched_getaffinity(0)
+            if cpus & allowed:
+                self.cpus, self.node = cpus & allowed, node
+        except Exception:
+            pass
+
+    def __enter__(self):
+        if self.cpus:
+            self.saved = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, self.cpus)
+        return self
+
+    def __exit__(self, *exc):
+        if self.saved is not None:
+            os.sched_setaffinity(0, self.saved)
+            self.saved = None
+        return False
+
+
 class ForkJoin:
     """Runs the two-stream entry points so that one timing stream sees all of the work:
     block work on the current stream, residue work on a side stream forked from and joined
@@ -828,10 +866,15 @@ def main():
     del C
     src = mine_e2e
     e_nnz, e_rows = src.nnz, src.m
-    h_rp, h_col, h_val = (t.cpu().pin_memory() for t in (src.row_ptr, src.col, src.val))
-    shard = n_vert // world
-    h_X = X[rank * shard:(rank + 1) * shard].cpu().pin_memory() if world > 1 else X.cpu().pin_memory()
-    h_C = torch.empty((e_rows, N_DENSE), dtype=torch.float32).pin_memory()
+    # The pinned host buffers are allocated and first touched while this process is bound to the
+    # CPUs of the GPU's own NUMA node, so that their pages sit in the memory next to the GPU's
+    # PCIe root (otherwise the copies of half the GPUs of a two-socket host cross the socket link).
+    numa = NumaBinding(dev)
+    with numa:
+        h_rp, h_col, h_val = (t.cpu().pin_memory() for t in (src.row_ptr, src.col, src.val))
+        shard = n_vert // world
+        h_X = X[rank * shard:(rank + 1) * shard].cpu().pin_memory() if world > 1 else X.cpu().pin_memory()
+        h_C = torch.zeros((e_rows, N_DENSE), dtype=torch.float32).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in (h_rp, h_col, h_val, h_X))
     d2h = h_C.numel() * 4
     # workspace for the split rows of the end-to-end slice (an application knows its matrix: sized once)
@@ -958,6 +1001,7 @@ def main():
            "d2h_bytes_per_step": int(sum(r["d2h_bytes"] for r in per_rank)),
            "bytes_are": "sums over all ranks; per_rank has each rank's share",
            "steps": args.e2e_steps, "per_rank": per_rank,
+           "host_buffers_numa_node": numa.node,
            "slowest_rank": {"rank": slowest["rank"],
                             "bound_by": ("h2d" if slowest["h2d_alone_ms"] >= slowest["d2h_alone_ms"] else "d2h"),
                             "copy_floor_ms": slowest["both_directions_ms"],
