@@ -87,7 +87,7 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--scale", type=int, default=23, help="R-MAT scale of the headline workload")
     p.add_argument("--no-extra", action="store_true", help="skip the secondary configs and the CPU baseline")
-    p.add_argument("--e2e-steps", type=int, default=10)
+    p.add_argument("--e2e-steps", type=int, default=20)
     p.add_argument("--repeats", type=int, default=0,
                    help="timed repeats of the --steps loop (0 = at least 10 and at least one second of device time)")
     p.add_argument("--e2e-row-weight", type=float, default=64.0,
