@@ -204,14 +204,21 @@ __device__ __forceinline__ unsigned hot_word(const unsigned *hot, int c) { retur
 __device__ __forceinline__ int tag_hot(int c, unsigned word) {
     return c | static_cast<int>(((word >> (c & 31)) & 1u) << 31);
 }
+// Where the dense row of column c (0 <= c < 2^31) starts, seen from a lane's base pointer: one
+// 32 x 32 -> 64 bit multiply by the row's byte length instead of 64-bit index arithmetic per gather.
+template <typename V>
+__device__ __forceinline__ const V *dense_row(const V *lane_base, unsigned c, unsigned row_bytes) {
+    return reinterpret_cast<const V *>(reinterpret_cast<const char *>(lane_base) +
+                                       static_cast<unsigned long long>(c) * row_bytes);
+}
 // Gather of the dense-row vector of a column: plain read-only load, or steered by the mark.
 template <bool kHints, typename V>
-__device__ __forceinline__ V gather(const V *lane_base, int c, size_t row_vecs, const GatherPolicy &policy) {
+__device__ __forceinline__ V gather(const V *lane_base, int c, unsigned row_bytes, const GatherPolicy &policy) {
     if constexpr (kHints) {
-        return ld_dense_policy(lane_base + static_cast<size_t>(c & 0x7fffffff) * row_vecs,
+        return ld_dense_policy(dense_row(lane_base, static_cast<unsigned>(c) & 0x7fffffffu, row_bytes),
                                c < 0 ? policy.hot : policy.cold);
     } else {
-        return ld_dense(lane_base + static_cast<size_t>(c) * row_vecs);
+        return ld_dense(dense_row(lane_base, static_cast<unsigned>(c), row_bytes));
     }
 }
 
