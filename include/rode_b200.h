@@ -121,9 +121,11 @@ int rode_preprocess_cpu(int seg_len, int k_block, int vec_len, int M, const int 
  * SpMM:  C[M x n] = S[M x k] * B[k x n], S in CSR + RoDe metadata, B and C row-major.
  *
  * Replaces RoDeSpmm_n32 / RoDeSpmm_n128 (RoDe_SpMM/RoDeSpmm.h:4-14, launcher
- * RoDe_SpMM/RoDeSpmm.cu:492-529).  One call serves every width: n must be a multiple of
- * 32 elements for float, 16 for double.  Block segments run on stream1, pure-residue rows
- * on stream2; the caller synchronises both, as with the reference.
+ * RoDe_SpMM/RoDeSpmm.cu:492-529).  One call serves every width: n may be any multiple
+ * of 4 columns, float or double.  Multiples of 32 (float) or 16 (double) are covered by whole
+ * lane-group tiles as in the reference; other widths, which the reference does not serve, leave
+ * part of the last tile idle and take no popularity hints.  Block segments run on stream1,
+ * pure-residue rows on stream2; the caller synchronises both, as with the reference.
  *
  * Differences a caller can observe: every row with at least one nonzero is WRITTEN (not
  * accumulated), without floating-point atomics, so results are deterministic.  Rows without

@@ -124,7 +124,9 @@ constexpr int kLoadsInFlight = 8;
 // lane: 8 -> 32 CTAs (64 registers), 12 -> 25 (80), 16 -> 20 (96), more -> no limit.
 constexpr int min_ctas_per_sm(int loads) { return loads <= 8 ? 32 : loads <= 12 ? 25 : loads <= 16 ? 20 : 1; }
 
-template <typename T, int VB, int L, int VPL, int U, int W, bool kHints, bool kClaim>
+// kRagged: the width is not a multiple of the tile; the last tile's lanes beyond the row's end neither
+// load nor store (widths the reference's tiles do not serve: any multiple of 4 columns).
+template <typename T, int VB, int L, int VPL, int U, int W, bool kHints, bool kClaim, bool kRagged>
 __global__ void __launch_bounds__(32 * W, min_ctas_per_sm(U * VPL * VB / 16) / W)
 spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
            const int *__restrict__ row_offsets, const int *__restrict__ block_r_ind,
@@ -156,6 +158,7 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     const unsigned row_bytes = static_cast<unsigned>(n) * static_cast<unsigned>(sizeof(T));  // n < 2^21 elements
     const size_t col_vec = static_cast<size_t>(blockIdx.y) * L * VPL + l;  // + v * L for vector v
     const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
+    auto inside = [&](int v) { return !kRagged || col_vec + v * L < row_vecs; };
     GatherPolicy policy = {};
     // the word after the bitmap is the library's verdict on this matrix (0: marks would not help)
     if constexpr (kHints) policy = make_gather_policy(__ldg(hot + hot_flag_word) != 0u);
@@ -234,7 +237,7 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
 #pragma unroll
                 for (int v = 0; v < VPL; ++v) {
                     buf[u][v] = vzero(static_cast<V *>(nullptr));
-                    if (t < cnt) buf[u][v] = gather<kHints>(b_lane + v * L, cc[u], row_bytes, policy);
+                    if (t < cnt && inside(v)) buf[u][v] = gather<kHints>(b_lane + v * L, cc[u], row_bytes, policy);
                 }
             }
 #pragma unroll
@@ -256,6 +259,7 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
     if (g == 0) {
 #pragma unroll
         for (int v = 0; v < VPL; ++v) {
+            if (!inside(v)) continue;
             if (whole_row)
                 st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec + v * L, acc[v]);
             else
@@ -359,7 +363,7 @@ spmm_fixup(int m1, int n, const int *__restrict__ row_offsets, const int *__rest
 // ---------------------------------------------------------------------------------------
 // Residue rows without a block part.  One lane group per L consecutive entries of
 // residue_r_ind; grid.y walks the column tiles.
-template <typename T, int L>
+template <typename T, int L, bool kRagged>
 __global__ void __launch_bounds__(kCtaThreads, (sizeof(T) == 4 ? 32 : 16) / kCtaWarps)  // fp32: 64 registers
 spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
           const int *__restrict__ column_indices, const int *__restrict__ row_offsets,
@@ -419,6 +423,7 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
     const size_t col_vec = static_cast<size_t>(blockIdx.y) * L + l;
     const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
     V *c_lane = reinterpret_cast<V *>(C) + col_vec;
+    const bool inside = !kRagged || col_vec < row_vecs;  // ragged widths: lanes beyond the row's end idle
 
     // Rows of the list without a nonzero are left alone: C arrives zero-filled (the contract of
     // the reference's entry points), and on graphs with many empty rows the zero rows were half
@@ -484,14 +489,14 @@ spmm_rows(int m2, int rows_per_group, int n, const T *__restrict__ values,
                     vv[u] = __shfl_sync(gmask, v_cur, t, L);
                 }
                 buf[u] = vzero(static_cast<V *>(nullptr));
-                if (t < cnt) buf[u] = ld_dense(dense_row(b_lane, static_cast<unsigned>(cc[u]), row_bytes));
+                if (t < cnt && inside) buf[u] = ld_dense(dense_row(b_lane, static_cast<unsigned>(cc[u]), row_bytes));
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 vfma(acc, vv[u], buf[u]);
                 ++pos;
                 if (pos == cur_end) {  // the stream passed the end of a row: store it, start the next
-                    st_stream(c_lane + static_cast<size_t>(cur_row) * row_vecs, acc);
+                    if (inside) st_stream(c_lane + static_cast<size_t>(cur_row) * row_vecs, acc);
                     acc = vzero(static_cast<V *>(nullptr));
                     if (todo) {
                         cur = __ffs(todo) - 1;
@@ -529,7 +534,7 @@ constexpr int kRowsCtaThreads = RODE_SPMM_ROWS_CTA;
 #define RODE_SPMM_WIDE_ROWS_WAVES 2
 #endif
 
-template <typename T, int VB, int L, int VPL>
+template <typename T, int VB, int L, int VPL, bool kRagged>
 __global__ void __launch_bounds__(kRowsCtaThreads, 1024 / kRowsCtaThreads)  // 64 registers: 32 warps per SM
 spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
                  const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind,
@@ -559,6 +564,7 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
     const size_t row_vecs = static_cast<size_t>(n) / kLen;
     const size_t col_vec = static_cast<size_t>(blockIdx.y) * L * VPL + l;
     const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
+    auto inside = [&](int v) { return !kRagged || col_vec + v * L < row_vecs; };
 
     V acc[VPL];
 #pragma unroll
@@ -615,7 +621,8 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
 #pragma unroll
                 for (int v = 0; v < VPL; ++v) {
                     bb[u][v] = vzero(static_cast<V *>(nullptr));
-                    if (t0 + u < cnt) bb[u][v] = ld_dense(b_lane + static_cast<size_t>(cc[u]) * row_vecs + v * L);
+                    if (t0 + u < cnt && inside(v))
+                        bb[u][v] = ld_dense(b_lane + static_cast<size_t>(cc[u]) * row_vecs + v * L);
                 }
 #pragma unroll
             for (int u = 0; u < U; ++u)
@@ -626,7 +633,7 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
     }
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
-        st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec + v * L, acc[v]);
+        if (inside(v)) st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec + v * L, acc[v]);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -636,7 +643,7 @@ spmm_rows_simple(int m2, int n, const T *__restrict__ values, const int *__restr
 // every (32 / L)-th nonzero each, so that all gathers of the row are in flight at once (L
 // per group), and a butterfly over the groups adds the partial rows.  Two dependent memory
 // round trips after the row's bounds are known, against up to 32 / L in spmm_rows_simple.
-template <typename T, int VB, int L, int VPL>
+template <typename T, int VB, int L, int VPL, bool kRagged>
 __global__ void __launch_bounds__(32 * kSmallGridWarps, 1)
 spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restrict__ column_indices,
                const int *__restrict__ row_offsets, const int *__restrict__ residue_r_ind,
@@ -669,6 +676,7 @@ spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restric
     const unsigned row_bytes = static_cast<unsigned>(n) * static_cast<unsigned>(sizeof(T));  // n < 2^21 elements
     const size_t col_vec = static_cast<size_t>(blockIdx.y) * L * VPL + l;
     const V *b_lane = reinterpret_cast<const V *>(B) + col_vec;
+    auto inside = [&](int v) { return !kRagged || col_vec + v * L < row_vecs; };
 
     int cc[L];
     T vv[L];
@@ -683,7 +691,7 @@ spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restric
 #pragma unroll
         for (int v = 0; v < VPL; ++v) {
             bb[t][v] = vzero(static_cast<V *>(nullptr));
-            if (t * G + g < len) bb[t][v] = ld_dense(dense_row(b_lane, static_cast<unsigned>(cc[t]), row_bytes) + v * L);
+            if (t * G + g < len && inside(v)) bb[t][v] = ld_dense(dense_row(b_lane, static_cast<unsigned>(cc[t]), row_bytes) + v * L);
         }
     V acc[VPL];
 #pragma unroll
@@ -697,17 +705,17 @@ spmm_rows_wide(int m2, int n, const T *__restrict__ values, const int *__restric
     if (g == 0) {
 #pragma unroll
         for (int v = 0; v < VPL; ++v)
-            st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec + v * L, acc[v]);
+            if (inside(v)) st_stream(reinterpret_cast<V *>(C) + static_cast<size_t>(row) * row_vecs + col_vec + v * L, acc[v]);
     }
 }
 
-template <typename T, int VB, int L, int VPL>
+template <typename T, int VB, int L, int VPL, bool kRagged>
 int launch_rows(int m2, int n, const T *values, const int *col, const int *row_offsets, const int *residue_r_ind,
                 const T *B, T *C, int *counters, cudaStream_t s2);
 
 // Block kernel of shape (VB bytes per load, L lanes, VPL loads per lane) and residue-row kernel
 // of shape (RVB, RL, RVPL); both cover the same column tile.
-template <typename T, int VB, int L, int VPL, int RVB, int RL, int RVPL>
+template <typename T, int VB, int L, int VPL, int RVB, int RL, int RVPL, bool kRagged>
 int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, const int *row_offsets,
                  const int *block_r_ind, const int *residue_r_ind, const int *st_off, const T *B, T *C,
                  T *partial, int *counters, const unsigned *hot, cudaStream_t s1, cudaStream_t s2) {
@@ -717,7 +725,8 @@ int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, 
     constexpr int kChunkSteps = L;                               // nonzeros per group per chunk
     constexpr int kSmallCap = 32 * 16 / VB;                      // small grids: at most 512 bytes per lane in flight
     constexpr int USmall = (kChunkSteps * VPL <= kSmallCap) ? kChunkSteps : kSmallCap / VPL;
-    const unsigned tiles = static_cast<unsigned>(n / kTileWidth);
+    // ragged widths: the last tile is partly empty
+    const unsigned tiles = static_cast<unsigned>(kRagged ? (n + kTileWidth - 1) / kTileWidth : n / kTileWidth);
     if (m1 > 0) {
         // Fewer warps than two full waves of 32 per SM: the latency of the longest segment
         // rules, so batches are larger.  CTAs stay one warp: with 4-warp CTAs the Zipf matrix
@@ -743,19 +752,19 @@ int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, 
         // Popularity hints: block kernel of the 512-byte tile only.  In the residue-row kernel
         // the marks saved DRAM bytes (5.36 -> 4.79 GB on R-MAT scale 23) but the extra registers
         // cost more time than that returned (1.41 -> 1.52 ms).
-        if constexpr (L * VPL * VB == 512) {
+        if constexpr (L * VPL * VB == 512 && !kRagged) {
             if (hot && !small_grid) {
-                spmm_block<T, VB, L, VPL, U, kCtaWarps, true, true><<<grid, kCtaThreads, 0, s1>>>(
+                spmm_block<T, VB, L, VPL, U, kCtaWarps, true, true, false><<<grid, kCtaThreads, 0, s1>>>(
                     m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, hot, (k + 31) / 32, claim);
                 launched = true;
             }
         }
         if (launched) {
         } else if (small_grid && USmall > U) {
-            spmm_block<T, VB, L, VPL, USmall, kCtaWarps, false, false><<<grid, kCtaThreads, 0, s1>>>(
+            spmm_block<T, VB, L, VPL, USmall, kCtaWarps, false, false, kRagged><<<grid, kCtaThreads, 0, s1>>>(
                 m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0, claim);
         } else {
-            spmm_block<T, VB, L, VPL, U, kCtaWarps, false, true><<<grid, kCtaThreads, 0, s1>>>(
+            spmm_block<T, VB, L, VPL, U, kCtaWarps, false, true, kRagged><<<grid, kCtaThreads, 0, s1>>>(
                 m1, n, values, col, row_offsets, block_r_ind, st_off, B, C, partial, nullptr, 0, claim);
         }
         RODE_CHECK_LAUNCH("rode::spmm_block");
@@ -777,15 +786,15 @@ int launch_shape(int m1, int m2, int k, int n, const T *values, const int *col, 
         RODE_CHECK_LAUNCH("rode::spmm_fixup");
     }
     if (m2 > 0)
-        return launch_rows<T, RVB, RL, RVPL>(m2, n, values, col, row_offsets, residue_r_ind, B, C, counters, s2);
+        return launch_rows<T, RVB, RL, RVPL, kRagged>(m2, n, values, col, row_offsets, residue_r_ind, B, C, counters, s2);
     return RODE_OK;
 }
 
-template <typename T, int VB, int L, int VPL>
+template <typename T, int VB, int L, int VPL, bool kRagged>
 int launch_rows(int m2, int n, const T *values, const int *col, const int *row_offsets, const int *residue_r_ind,
                 const T *B, T *C, int *counters, cudaStream_t s2) {
     constexpr int kTileWidth = L * VPL * VecB<T, VB>::kLen;
-    const unsigned tiles = static_cast<unsigned>(n / kTileWidth);
+    const unsigned tiles = static_cast<unsigned>(kRagged ? (n + kTileWidth - 1) / kTileWidth : n / kTileWidth);
     {
         if constexpr (VB == 16 && L == 32 && VPL == 1) {
             // 32 rows per warp when the list is long; fewer (shorter dependent chains, more
@@ -806,16 +815,16 @@ int launch_rows(int m2, int n, const T *values, const int *col, const int *row_o
                 RODE_CUDA_TRY(cudaMemsetAsync(claim, 0, sizeof(int) * tiles, s2));
             }
             dim3 grid(static_cast<unsigned>(persistent ? (resident + tiles - 1) / tiles : ctas_needed), tiles);
-            spmm_rows<T, 32><<<grid, kCtaThreads, 0, s2>>>(m2, per_group, n, values, col, row_offsets,
+            spmm_rows<T, 32, kRagged><<<grid, kCtaThreads, 0, s2>>>(m2, per_group, n, values, col, row_offsets,
                                                            residue_r_ind, B, C, claim);
         } else if (static_cast<long long>(m2) * tiles <= RODE_SPMM_WIDE_ROWS_WAVES * 32LL * sm_count()) {
             dim3 grid((m2 + kSmallGridWarps - 1) / kSmallGridWarps, tiles);
-            spmm_rows_wide<T, VB, L, VPL><<<grid, 32 * kSmallGridWarps, 0, s2>>>(m2, n, values, col, row_offsets,
+            spmm_rows_wide<T, VB, L, VPL, kRagged><<<grid, 32 * kSmallGridWarps, 0, s2>>>(m2, n, values, col, row_offsets,
                                                                                  residue_r_ind, B, C);
         } else {
             constexpr int kRowsPerCta = kRowsCtaThreads / L;
             dim3 grid((m2 + kRowsPerCta - 1) / kRowsPerCta, tiles);
-            spmm_rows_simple<T, VB, L, VPL><<<grid, kRowsCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets,
+            spmm_rows_simple<T, VB, L, VPL, kRagged><<<grid, kRowsCtaThreads, 0, s2>>>(m2, n, values, col, row_offsets,
                                                                               residue_r_ind, B, C);
         }
         RODE_CHECK_LAUNCH("rode::spmm_rows");
@@ -837,15 +846,14 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
     if (hot != nullptr && k <= 0)
         return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: k (the number of columns the bitmap covers) must be positive "
                                                "when hot_columns is given");
-    if (n % (8 * kLen) != 0)
-        return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: n = %d is not a multiple of %d", n, 8 * kLen);
+    if (n % 4 != 0) return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: n = %d is not a multiple of 4", n);
     if (m1 == 0 && m2 == 0) return RODE_OK;
     if (!values || !col || !row_offsets || !B || !C) return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: null array");
     if (m1 > 0 && (!block_r_ind || !st_off)) return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: null block metadata");
     if (m2 > 0 && !residue_r_ind) return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: null residue metadata");
     if (!aligned_to(B, 16) || !aligned_to(C, 16))
         return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: B and C must be 16-byte aligned");
-    if (n / (8 * kLen) > 65535)
+    if ((n + 8 * kLen - 1) / (8 * kLen) > 65535)
         return fail(RODE_ERR_INVALID_ARGUMENT, "spmm: n = %d exceeds the supported width (%d)", n, 65535 * 8 * kLen);
     size_t need = 0;
     rode_spmm_workspace_bytes(m1, n, static_cast<int>(sizeof(T)), &need);
@@ -864,17 +872,26 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
     // Widest tile (32, 16 or 8 vectors of 16 bytes) that divides the row.  Shapes are given in
     // 16-byte vectors; with 32-byte loads (operands 32-byte aligned) a group has half the lanes.
     // The batched residue kernel of the widest tile (shape 3201) always loads 16 bytes per lane.
-#define RODE_LAUNCH16(shape, rows_shape)                                                                        \
-    launch_shape<T, 16, (shape) / 100, (shape) % 100, 16, (rows_shape) / 100, (rows_shape) % 100>(              \
+#define RODE_LAUNCH16(shape, rows_shape) RODE_LAUNCH16R(shape, rows_shape, false)
+#define RODE_LAUNCH16R(shape, rows_shape, ragged)                                                               \
+    launch_shape<T, 16, (shape) / 100, (shape) % 100, 16, (rows_shape) / 100, (rows_shape) % 100, ragged>(      \
         m1, m2, k, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, counters, hot, stream1, \
         stream2)
 #define RODE_LAUNCH32(shape, rows_shape, rows_bytes)                                                             \
     launch_shape<T, 32, wide_lanes(shape), wide_vpl(shape), rows_bytes,                                          \
                  (rows_bytes) == 32 ? wide_lanes(rows_shape) : (rows_shape) / 100,                               \
-                 (rows_bytes) == 32 ? wide_vpl(rows_shape) : (rows_shape) % 100>(                                \
+                 (rows_bytes) == 32 ? wide_vpl(rows_shape) : (rows_shape) % 100, false>(                         \
         m1, m2, k, n, values, col, row_offsets, block_r_ind, residue_r_ind, st_off, B, C, partial, counters, hot, stream1, \
         stream2)
     const int vecs = n / kLen;
+    // Widths the tiles do not divide (any other multiple of 4 columns; the reference has none of
+    // them): the narrowest shape that covers the row, or 512-byte tiles with a partly empty last
+    // one.  Always 16-byte loads, no popularity hints.
+    if (vecs % 8 != 0) {
+        if (vecs < 8) return RODE_LAUNCH16R(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8, true);
+        if (vecs < 16) return RODE_LAUNCH16R(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16, true);
+        return RODE_LAUNCH16R(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32, true);
+    }
     // 32-byte loads measured no faster than 16-byte ones on any benchmark matrix (the gathers are
     // bound by bytes through L1/L2, not by load instructions), so the default build does not
     // instantiate them.
@@ -893,6 +910,7 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
     if (vecs % 16 == 0) return RODE_LAUNCH16(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16);
     return RODE_LAUNCH16(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8);
 #undef RODE_LAUNCH16
+#undef RODE_LAUNCH16R
 #undef RODE_LAUNCH32
 }
 

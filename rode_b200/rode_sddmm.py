@@ -121,7 +121,7 @@ def rode_sddmm(sparse_matrix: RoDeCSR, lhs: torch.Tensor, rhs: torch.Tensor) -> 
 
 
 def rode_spmm(sparse_matrix: RoDeCSR, dense: torch.Tensor, hints: bool = True) -> torch.Tensor:
-    """C = S @ dense for dense [n, width], width a multiple of 32.  Needs metadata from
+    """C = S @ dense for dense [n, width], width a multiple of 4.  Needs metadata from
     seg_length 512 (k = 32 or 64 at construction); the reference has no Python SpMM.
 
     ``hints``: gather popular columns' rows with an L2 policy that keeps them resident

@@ -61,7 +61,7 @@ def test_argument_errors_are_reported_not_raised_by_cuda(built_library):
     # workspace too small
     assert lib.rode_preprocess(512, 32, 4, 5000, 16, 16, 16, 16, 16, 16, 16, 8, None) == capi.RODE_ERR_WORKSPACE
     # unsupported widths
-    assert lib.rode_spmm_f32(1, 1, 8, 20, 16, 16, 16, 16, 16, 16, 16, 16, None, 0, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
+    assert lib.rode_spmm_f32(1, 1, 8, 22, 16, 16, 16, 16, 16, 16, 16, 16, None, 0, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
     assert lib.rode_sddmm_f32(1, 1, 8, 50, 16, 16, 16, 16, 16, 16, 16, 16, 16, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
     assert lib.rode_sddmm_f32(1, 1, 8, 260, 16, 16, 16, 16, 16, 16, 16, 16, 16, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
     # misaligned dense operands (16-byte alignment is part of the contract)
@@ -98,7 +98,7 @@ def test_hot_columns_sizes_and_argument_errors(built_library):
     assert lib.rode_hot_columns(10, 64, 256, 512, 1, 256, 264, 1 << 20, None) == capi.RODE_ERR_WORKSPACE
     assert b"aligned" in lib.rode_last_error()
     # the hinted SpMM entry points validate like the plain ones
-    assert lib.rode_spmm_f32_hot(1, 1, 8, 20, 16, 16, 16, 16, 16, 16, 16, 16, None, 0, 16, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
+    assert lib.rode_spmm_f32_hot(1, 1, 8, 22, 16, 16, 16, 16, 16, 16, 16, 16, None, 0, 16, None, None) == capi.RODE_ERR_INVALID_ARGUMENT
     assert lib.rode_spmm_f64_hot(0, 0, 8, 32, None, None, None, None, None, None, None, None, None, 0, None, None, None) == 0
 
 

@@ -81,7 +81,8 @@ def test_argument_checks_mirror_the_reference(api):
 def test_rode_spmm_python_entry(api):
     dev = torch.device("cuda")
     torch.manual_seed(3)
-    for m, n, per_row, width in ((4096, 4096, 128, 128), (1999, 257, 45, 32), (1, 1000, 100, 64), (1000, 1, 1, 96)):
+    for m, n, per_row, width in ((4096, 4096, 128, 128), (1999, 257, 45, 32), (1, 1000, 100, 64), (1000, 1, 1, 96),
+                                 (3000, 3000, 70, 20), (3000, 3000, 70, 100)):   # widths no tile divides
         S = api.RoDeCSR.from_random(m, n, per_row, dev, k=32)
         X = torch.randn(n, width, device=dev)
         C = api.rode_spmm(S, X)

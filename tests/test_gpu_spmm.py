@@ -65,6 +65,45 @@ def test_spmm_other_widths(oracle_cpu, n):
     _check_against_truth(oracle_cpu, A, B.numpy(), C, f"n={n}")
 
 
+def test_spmm_widths_the_tiles_do_not_divide(oracle_cpu):
+    """Any multiple of 4 columns behind the one entry point (the reference serves multiples of its
+    32- or 64-wide tile only): the narrowest lane-group shape that covers the row, or 512-byte tiles
+    whose last one is partly empty.  A small matrix (small-grid kernels, one warp per residue row)
+    and one whose grids fill the GPU (batched and per-group residue kernels); C sits inside a larger
+    buffer whose guard words must survive."""
+    matrices = {
+        "zipf 2048 (small grids)": W.zipf_rows(m=2048, n=2048, cap=2048),
+        "pareto 65536 (full grids)": W.pareto_rows(m=1 << 16, n=1 << 16, cap=20000, seed=5),
+    }
+    for name, A in matrices.items():
+        d, meta = gpu_inputs(A)
+        assert meta.m1 > 0 and meta.m2 > 0
+        rp = A.row_ptr.numpy()
+        assert ((rp[1:] - rp[:-1]) > 600).any()  # rows cut into several segments: the fix-up grid runs
+        for n in (4, 8, 12, 20, 28, 36, 44, 100, 132, 200, 260):
+            B = W.dense(A.n, n, seed=n)
+            guard = 64
+            buf = torch.zeros(A.m * n + guard, device="cuda")
+            buf[A.m * n:] = 12345.0
+            C = buf[:A.m * n].view(A.m, n)
+            capi.spmm(meta, d.row_ptr, d.col, d.val, B.cuda(), C=C)
+            torch.cuda.synchronize()
+            assert bool((buf[A.m * n:] == 12345.0).all()), f"{name} n={n}: wrote past the end of C"
+            _check_against_truth(oracle_cpu, A, B.numpy(), C, f"{name} n={n}")
+    # double: 16-byte vectors hold two columns
+    A = matrices["zipf 2048 (small grids)"]
+    d, meta = gpu_inputs(A)
+    for n in (4, 12, 20, 36, 68, 132):
+        B = W.dense(A.n, n, seed=n, dtype=torch.float64)
+        C = capi.spmm(meta, d.row_ptr, d.col, d.val.double(), B.cuda())
+        truth = oracle_cpu.spmm_f64(A.row_ptr.numpy(), A.col.numpy(), A.val.numpy().astype(np.float64), B.numpy())
+        assert np.allclose(C.cpu().numpy(), truth, rtol=1e-12, atol=1e-12), n
+    # not a multiple of 4: refused
+    for n in (6, 30, 130):
+        with pytest.raises(capi.RodeError):
+            capi.spmm(meta, d.row_ptr, d.col, d.val, torch.zeros((A.n, n), device="cuda"))
+
+
 def test_spmm_edge_cases(oracle_cpu):
     def csr(lens, ncols, seed=0):
         rng = np.random.default_rng(seed)
