@@ -219,7 +219,7 @@ def time_loop(fn, steps, warmup, stream, flush=None):
 
 
 def time_preprocess(row_ptr, nnz, seg, iters, peak_gbs, with_host=True, with_swizzle=True):
-    """Device time of the three preprocessing kernels (raw entry point, buffers allocated
+    """Device time of the preprocessing kernels (raw entry point, buffers allocated
     once), the host twin's single-thread time, and the HBM roofline of the device version:
     algorithmic bytes = row pointer read once + outputs written once."""
     from rode_b200 import capi

@@ -8,7 +8,7 @@
  * and st_off and n_res entries of residue_r_ind, as the reference does: no end sentinel
  * st_off[n_blk], so buffers sized like the reference's callers size them (nnz / N_SEG + M
  * entries, Preprocess_opt/_preprocess.cu:426-430) are large enough.  The SpMM and SDDMM
- * entry points of this library never read st_off[n_blk].  Its scratch (8 bytes per 1024
+ * entry points of this library never read st_off[n_blk].  Its scratch (8 bytes per 2048
  * rows) comes from a buffer the library allocates on first use.
  * RoDe_preprocess_cpu: the single-thread host loop.  It also writes the sentinel
  * st_off[n_blk] = row_ptr[M], as the reference's copies of this loop in its SDDMM drivers do

@@ -83,7 +83,7 @@ int rode_preprocess(int seg_len, int k_block, int vec_len, int M, const int *row
 
 /* Same decomposition, same outputs, but the library allocates nothing and the caller brings
  * no workspace: the per-tile scratch lives in a fixed array inside the library's device
- * image (128 KB on every GPU that loads the library, kept until the process exits).
+ * image (64 KB on every GPU that loads the library, kept until the process exits).
  * This entry point has no counterpart in the reference.
  *
  * It is meant for callers that must not, or cannot, obtain device memory at call time:
@@ -103,9 +103,10 @@ int rode_preprocess(int seg_len, int k_block, int vec_len, int M, const int *row
  *             the life of the process: after a cudaDeviceReset in the same process it is
  *             stale, so do not call this entry point again after resetting a device.
  *   Sharing   all calls on a device use the same array and it keeps the previous call's
- *             contents.  Nothing needs clearing (every entry that is read is written first
- *             by the same call), but two calls that overlap in time on one GPU, e.g. on
- *             two streams, race on it: serialise them. */
+ *             contents.  The caller clears nothing (the call itself zeroes its 8-byte
+ *             counter with a memset node on the stream, and every other entry that is read is
+ *             written first by the same call), but two calls that overlap in time on one GPU,
+ *             e.g. on two streams, race on it: serialise them. */
 int rode_preprocess_noalloc(int seg_len, int k_block, int vec_len, int M, const int *row_ptr,
                             int *block_r_ind, int *st_off, int *residue_r_ind, int *n_blk, int *n_res,
                             rode_stream_t stream);

@@ -163,7 +163,7 @@ def preprocess(row_ptr: torch.Tensor, nnz: int, seg_len: int = 512, k_block: int
                stream=None, trim: bool = True) -> RodeMeta:
     """Device-side row decomposition of a CSR row pointer (int32 CUDA tensor [M+1]).
 
-    Allocates outputs at the capacity bound, runs the three kernels on ``stream`` (default:
+    Allocates outputs at the capacity bound, runs the two kernels on ``stream`` (default:
     torch's current stream), reads the two counts back (one 8-byte D2H copy, which
     synchronises the stream) and returns views trimmed to the counts."""
     _dev_i32(row_ptr, "row_ptr")

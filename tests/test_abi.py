@@ -42,7 +42,7 @@ def test_cpp_symbol_names_equal_the_reference_objects():
 def test_version_and_sizes(built_library):
     assert re.fullmatch(r"\d+\.\d+\.\d+", capi.version())
     assert capi.preprocess_workspace_bytes(0) == 8
-    assert capi.preprocess_workspace_bytes(1024) == 8
+    assert capi.preprocess_workspace_bytes(1024) == 16      # the CTA counter + one tile of 2048 rows
     assert capi.preprocess_workspace_bytes(1025) == 16
     # one partial row per block segment, rounded up to 256 bytes, plus 256 bytes of claim counters
     assert capi.spmm_workspace_bytes(10, 128, 4) == 10 * 128 * 4 + 256

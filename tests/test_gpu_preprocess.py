@@ -52,7 +52,7 @@ def test_gpu_preprocess_matches_oracle_on_matrix_families(oracle_cpu, family):
 
 def test_gpu_preprocess_tile_boundaries_and_long_rows(oracle_cpu):
     rng = np.random.default_rng(5)
-    for m in (1, 2, 1023, 1024, 1025, 2048, 4097):
+    for m in (1, 2, 1023, 1024, 1025, 2047, 2048, 2049, 4097, 6145):
         lens = rng.integers(0, 70, m)
         lens[rng.integers(0, m)] = 300000          # hundreds of segments in one row
         lens[-1] = 5000                            # long last row
@@ -63,13 +63,29 @@ def test_gpu_preprocess_tile_boundaries_and_long_rows(oracle_cpu):
 
 
 def test_gpu_preprocess_more_tiles_than_one_scan_pass(oracle_cpu):
-    """More than 8192 tiles of 1024 rows: the single-CTA tile scan needs a second pass."""
+    """More tiles (of 2048 rows) than the 2048 that the last CTA's scan takes per pass."""
     rng = np.random.default_rng(6)
     m = 8192 * 1024 + 5000
     lens = rng.integers(0, 40, m)
     lens[rng.integers(0, m, 50)] = 3000
     rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     _same(_gpu(rp, 512, 32, 4), oracle_cpu.preprocess(rp, 512, 32, 4))
+
+
+def test_gpu_preprocess_tiles_with_more_segments_than_the_staging_holds(oracle_cpu):
+    """A tile's segments are put in order in shared memory (2048 entries), rows of more than 8
+    segments by whole warps.  Tiles with more segments take the direct path; tiles next to them the
+    staged one."""
+    rng = np.random.default_rng(8)
+    m = 5 * 2048 + 77
+    lens = rng.integers(0, 70, m)
+    lens[100:420] = rng.integers(290, 900, 320)        # tile 0: 320 long rows, > 2048 segments at seg 32
+    lens[2048 + 5: 2048 + 40] = 330                     # tile 1: a few long rows, staged
+    lens[3 * 2048: 3 * 2048 + 2048] = 33                # tile 3: exactly one segment per row (2048: still staged)
+    lens[4 * 2048 + 9] = 70000                          # tile 4: one row of 2188 segments at seg 32
+    rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    for seg, kb, vec in PARAMS + ((64, 32, 4), (96, 24, 3)):
+        _same(_gpu(rp, seg, kb, vec), oracle_cpu.preprocess(rp, seg, kb, vec))
 
 
 def test_reference_signature_entry_point(oracle_cpu):
