@@ -100,8 +100,9 @@ def parse_args():
                         "library finds them useful")
     p.add_argument("--hint-budget-mb", type=float, default=0.0,
                    help="bytes of dense rows the hints may mark, in MB (0 = the library's default)")
-    p.add_argument("--only", choices=["spmm", "sddmm"], default=None,
-                   help="small single-op run (one family, one width) for profiling and A/B timing")
+    p.add_argument("--only", choices=["spmm", "sddmm", "preprocess"], default=None,
+                   help="small single-op run (one family, one width) for profiling and A/B timing; for "
+                        "preprocess --width is the segment length (512 or 32)")
     p.add_argument("--family", default="rmat", choices=["bernoulli", "zipf", "stencil", "pareto", "rmat"])
     p.add_argument("--width", type=int, default=128, help="N of SpMM / K of SDDMM for --only")
     p.add_argument("--size", type=float, default=1.0, help="row-count factor of the family for --only")
@@ -561,6 +562,11 @@ def single_op(args):
     peak_gbs, peak_kind = measured_peak()
     A = make_family(args.family, dev, args.scale, args.size)
     width = args.width
+    if args.only == "preprocess":
+        # `steps` calls back to back on pre-allocated buffers (the raw entry point), as the full run times it
+        seg = width if width in (32, 512) else 512
+        pre = time_preprocess(A.row_ptr, A.nnz, seg, args.steps, peak_gbs, with_host=False, with_swizzle=False)
+        return {"only": "preprocess", "family": args.family, **pre, "peak_kind": peak_kind}
     seg = 32 if (args.only == "sddmm" and width == 128) else 512
     meta = capi.preprocess(A.row_ptr, A.nnz, seg, 32, 4)
     fj = ForkJoin(dev)
