@@ -43,6 +43,7 @@
 // Per nonzero the kernels move 8 B of CSR data and 16*L bytes of the dense operand (from
 // L1/L2/HBM depending on reuse); per row 4*n bytes of C.  Dense-row offsets are 64-bit.
 #include <climits>
+#include <type_traits>
 
 #include "rode_common.cuh"
 
@@ -95,6 +96,10 @@ constexpr int kSmallGridWarps = RODE_SPMM_WIDE_ROWS_CTA_WARPS;  // rows (warps) 
 // data path, where a shuffle costs as much as 128 bytes of gathered data.
 #ifndef RODE_SPMM_PAIRS_IN_SMEM
 #define RODE_SPMM_PAIRS_IN_SMEM 1
+#endif
+// Block kernel: a separate unpredicated form for full chunks of 32 nonzeros (1) or one predicated form (0).
+#ifndef RODE_SPMM_FULL_CHUNK_PATH
+#define RODE_SPMM_FULL_CHUNK_PATH 1
 #endif
 // Claim counters of the persistent block kernel: one int per column tile, at the end of the workspace.
 constexpr size_t kCounterBytes = 256;
@@ -217,34 +222,55 @@ spmm_block(int m1, int n, const T *__restrict__ values, const int *__restrict__ 
             s_val[warp_in_cta][stage_buf][stage_slot] = v_cur;
             __syncwarp();
         }
+        // One chunk of the batched gather.  A full chunk (every chunk of a segment but its last) can take
+        // a form without bounds: no predicate per gather and no zero-fill of the row buffers (ncu counted
+        // 23 warp instructions per gathered row in the predicated form: 4 FMA, 1 load, the rest address,
+        // policy, predicate and zero-fill work).
+        auto chunk = [&](auto full_tag) {
+            constexpr bool kFullChunk = decltype(full_tag)::value;
 #pragma unroll
-        for (int b = 0; b < NB; ++b) {
-            if (b * U * G >= cnt) break;  // warp-uniform
-            V buf[U][VPL];
-            T vv[U];
-            int cc[U];
-            if constexpr (kStage) {
-                ld_shared_run<U>(&s_col[warp_in_cta][stage_buf][g * kSteps + b * U], cc);
-                ld_shared_run<U>(&s_val[warp_in_cta][stage_buf][g * kSteps + b * U], vv);
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int t = (b * U + u) * G + g;  // position inside the chunk
-                if constexpr (!kStage) {
-                    cc[u] = __shfl_sync(kFull, c_cur, t & 31);
-                    vv[u] = __shfl_sync(kFull, v_cur, t & 31);
+            for (int b = 0; b < NB; ++b) {
+                if constexpr (!kFullChunk) {
+                    if (b * U * G >= cnt) break;  // warp-uniform
+                }
+                V buf[U][VPL];
+                T vv[U];
+                int cc[U];
+                if constexpr (kStage) {
+                    ld_shared_run<U>(&s_col[warp_in_cta][stage_buf][g * kSteps + b * U], cc);
+                    ld_shared_run<U>(&s_val[warp_in_cta][stage_buf][g * kSteps + b * U], vv);
                 }
 #pragma unroll
-                for (int v = 0; v < VPL; ++v) {
-                    buf[u][v] = vzero(static_cast<V *>(nullptr));
-                    if (t < cnt && inside(v)) buf[u][v] = gather<kHints>(b_lane + v * L, cc[u], row_bytes, policy);
+                for (int u = 0; u < U; ++u) {
+                    const int t = (b * U + u) * G + g;  // position inside the chunk
+                    if constexpr (!kStage) {
+                        cc[u] = __shfl_sync(kFull, c_cur, t & 31);
+                        vv[u] = __shfl_sync(kFull, v_cur, t & 31);
+                    }
+#pragma unroll
+                    for (int v = 0; v < VPL; ++v) {
+                        if constexpr (kFullChunk && !kRagged) {
+                            buf[u][v] = gather<kHints>(b_lane + v * L, cc[u], row_bytes, policy);
+                        } else {
+                            buf[u][v] = vzero(static_cast<V *>(nullptr));
+                            if ((kFullChunk || t < cnt) && inside(v))
+                                buf[u][v] = gather<kHints>(b_lane + v * L, cc[u], row_bytes, policy);
+                        }
+                    }
                 }
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+#pragma unroll
+                    for (int v = 0; v < VPL; ++v) vfma(acc[v], vv[u], buf[u][v]);
             }
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int v = 0; v < VPL; ++v) vfma(acc[v], vv[u], buf[u][v]);
-        }
+        };
+        // (only the 512-byte tile of large grids: R-MAT 21 N = 128 block kernel 0.818 -> 0.787 ms, R-MAT 23
+        // step 4.76 -> 4.62 ms; the narrower shapes and the small-grid form measured 1-2 % slower with it)
+        constexpr bool kFullChunkPath = RODE_SPMM_FULL_CHUNK_PATH != 0 && L == 32 && U == kLoadsInFlight / VPL;
+        if (kFullChunkPath && cnt == 32)
+            chunk(std::true_type{});
+        else
+            chunk(std::false_type{});
         c_cur = kHints ? tag_hot(c_nxt, w_nxt) : c_nxt;
         v_cur = v_nxt;
         c_nxt = c_pre;
