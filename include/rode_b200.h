@@ -67,7 +67,8 @@ const char *rode_version(void);
  *   residue_r_ind         device, capacity >= min(M, n_res)
  *   n_blk, n_res          device int32[1] each
  *   workspace             device scratch of rode_preprocess_workspace_bytes(M) bytes,
- *                         256-byte aligned; contents are don't-care before and after
+ *                         256-byte aligned; contents are don't-care before and after;
+ *                         calls that may run at the same time need a workspace each
  * Unlike the reference, outputs are never used as scratch, so there is no in-place
  * hazard between thread blocks.
  */
