@@ -5,8 +5,8 @@
 // (block segments, residue rows); how the work is done is new:
 //
 //  * A dense-row slice of the column tile (8, 16 or 32 vectors of 16 bytes) is covered by a
-//    lane group of L lanes with VPL vectors per lane (LDG.128 each): 4 x 2 for 8 vectors,
-//    8 x 2 for 16, 32 x 1 for 32.  Two vectors per lane halve the shuffles and the address
+//    lane group of L lanes with VPL vectors per lane (LDG.128 each): 4 x 2 for 8 vectors (8 x 1 in
+//    the block kernel), 8 x 2 for 16, 32 x 1 for 32.  Two vectors per lane halve the shuffles and the address
 //    arithmetic per byte (measured: N = 32 power-law 0.68 -> 0.58 ms, N = 64 R-MAT-21
 //    0.99 -> 0.75 ms, N = 64 stencil 0.97 -> 0.75 ms; for 32 vectors no shape beat 32 x 1).
 //    A warp holds G = 32/L lane groups.
@@ -64,8 +64,16 @@ constexpr int kSmallGridWarps = RODE_SPMM_WIDE_ROWS_CTA_WARPS;  // rows (warps) 
 
 // Shape of a lane group per tile width (in 16-byte vectors: 8, 16 or 32 per dense-row slice):
 // L lanes x VPL vectors per lane, encoded as L * 100 + VPL.
+// (8 x 1 in the block kernel of the 128-byte tile: a load instruction then covers whole 128-byte lines, 4
+// rows per warp, where 4 x 2 covers 8 half lines.  R-MAT 23 N = 32 block kernel 2.19 -> 1.20 ms, R-MAT 21
+// N = 96 1.43 -> 0.92 ms, Zipf N = 32 -7 %; uniformly random columns lose 3 %: Pareto 2^20 N = 32 0.354 ->
+// 0.365 ms.  The per-row residue kernels measured faster with 4 x 2: R-MAT 23 N = 32 0.756 against 1.079 ms.)
 #ifndef RODE_SPMM_SHAPE_8
-#define RODE_SPMM_SHAPE_8 402
+#define RODE_SPMM_SHAPE_8 801
+#endif
+// Residue rows of 8-vector tiles (spmm_rows_simple, spmm_rows_wide) may use another shape than the block kernel.
+#ifndef RODE_SPMM_ROWS_SHAPE_8
+#define RODE_SPMM_ROWS_SHAPE_8 402
 #endif
 #ifndef RODE_SPMM_SHAPE_16
 #define RODE_SPMM_SHAPE_16 802
@@ -914,7 +922,7 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
     // them): the narrowest shape that covers the row, or 512-byte tiles with a partly empty last
     // one.  Always 16-byte loads, no popularity hints.
     if (vecs % 8 != 0) {
-        if (vecs < 8) return RODE_LAUNCH16R(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8, true);
+        if (vecs < 8) return RODE_LAUNCH16R(RODE_SPMM_SHAPE_8, RODE_SPMM_ROWS_SHAPE_8, true);
         if (vecs < 16) return RODE_LAUNCH16R(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16, true);
         return RODE_LAUNCH16R(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32, true);
     }
@@ -929,12 +937,12 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
                 return RODE_LAUNCH32(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32, 32);
             }
             if (vecs % 16 == 0) return RODE_LAUNCH32(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16, 32);
-            return RODE_LAUNCH32(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8, 32);
+            return RODE_LAUNCH32(RODE_SPMM_SHAPE_8, RODE_SPMM_ROWS_SHAPE_8, 32);
         }
     }
     if (vecs % 32 == 0 && RODE_SPMM_MAX_TILE_VECS >= 32) return RODE_LAUNCH16(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32);
     if (vecs % 16 == 0) return RODE_LAUNCH16(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16);
-    return RODE_LAUNCH16(RODE_SPMM_SHAPE_8, RODE_SPMM_SHAPE_8);
+    return RODE_LAUNCH16(RODE_SPMM_SHAPE_8, RODE_SPMM_ROWS_SHAPE_8);
 #undef RODE_LAUNCH16
 #undef RODE_LAUNCH16R
 #undef RODE_LAUNCH32
