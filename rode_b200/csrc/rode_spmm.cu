@@ -92,6 +92,13 @@ constexpr int kSmallGridWarps = RODE_SPMM_WIDE_ROWS_CTA_WARPS;  // rows (warps) 
 #ifndef RODE_SPMM_MAX_TILE_VECS
 #define RODE_SPMM_MAX_TILE_VECS 32
 #endif
+// 128-byte tile (N = 32 floats, 16 doubles) with one 32-byte load per lane and 4 lanes per dense row (1) or
+// with the 16-byte shapes above (0).  Stencil 128^3 N = 32 0.510 -> 0.401 ms (a load instruction of the
+// per-row kernel covers whole lines of 8 rows instead of half lines); the other matrices measure the same
+// as with the 8 x 1 block shape.
+#ifndef RODE_SPMM_TILE8_WIDE_LOADS
+#define RODE_SPMM_TILE8_WIDE_LOADS 1
+#endif
 // Bytes per load instruction of a lane in the block kernel and the per-row residue kernels:
 // 16 (LDG.128) or 32 (the 256-bit loads of sm_100).  The shapes above are given in 16-byte
 // vectors; with 32-byte loads a lane group has half as many lanes.
@@ -942,6 +949,14 @@ int spmm(int m1, int m2, int k, int n, const T *values, const int *col, const in
     }
     if (vecs % 32 == 0 && RODE_SPMM_MAX_TILE_VECS >= 32) return RODE_LAUNCH16(RODE_SPMM_SHAPE_32, RODE_SPMM_ROWS_SHAPE_32);
     if (vecs % 16 == 0) return RODE_LAUNCH16(RODE_SPMM_SHAPE_16, RODE_SPMM_SHAPE_16);
+    // 128-byte tile: 4 lanes x one 32-byte load cover a whole line per dense row and 8 rows per warp, in
+    // the block and the per-row residue kernels alike (operands 32-byte aligned; else the 16-byte shapes)
+    if constexpr (RODE_SPMM_TILE8_WIDE_LOADS != 0) {
+        if (aligned_to(B, 32) && aligned_to(C, 32) && aligned_to(workspace, 32))
+            return launch_shape<T, 32, 4, 1, 32, 4, 1, false>(m1, m2, k, n, values, col, row_offsets, block_r_ind,
+                                                              residue_r_ind, st_off, B, C, partial, counters, hot,
+                                                              stream1, stream2);
+    }
     return RODE_LAUNCH16(RODE_SPMM_SHAPE_8, RODE_SPMM_ROWS_SHAPE_8);
 #undef RODE_LAUNCH16
 #undef RODE_LAUNCH16R

@@ -104,6 +104,28 @@ def test_spmm_widths_the_tiles_do_not_divide(oracle_cpu):
             capi.spmm(meta, d.row_ptr, d.col, d.val, torch.zeros((A.n, n), device="cuda"))
 
 
+def test_spmm_operands_aligned_to_16_bytes_only(oracle_cpu):
+    """The 128-byte tile uses 32-byte loads when B, C and the workspace are 32-byte aligned and the
+    16-byte shapes otherwise (other lane groups, so another summation order): both against the oracle."""
+    A = W.pareto_rows(m=20000, n=20000, cap=3000, seed=11)
+    d, meta = gpu_inputs(A)
+    for n in (32, 96):
+        B = W.dense(A.n, n, seed=12)
+        Bd = B.cuda()
+        assert Bd.data_ptr() % 32 == 0
+        C_wide = capi.spmm(meta, d.row_ptr, d.col, d.val, Bd)
+        _check_against_truth(oracle_cpu, A, B.numpy(), C_wide, f"32-byte aligned n={n}")
+        buf_b = torch.empty(A.n * n + 4, device="cuda")
+        B16 = buf_b[4:].view(A.n, n)
+        B16.copy_(Bd)
+        buf_c = torch.zeros(A.m * n + 4, device="cuda")
+        C16 = buf_c[4:].view(A.m, n)
+        assert B16.data_ptr() % 32 == 16 and C16.data_ptr() % 32 == 16
+        capi.spmm(meta, d.row_ptr, d.col, d.val, B16, C=C16)
+        _check_against_truth(oracle_cpu, A, B.numpy(), C16, f"16-byte aligned n={n}")
+        assert float(buf_c[:4].abs().sum()) == 0.0
+
+
 def test_spmm_edge_cases(oracle_cpu):
     def csr(lens, ncols, seed=0):
         rng = np.random.default_rng(seed)
