@@ -87,6 +87,21 @@ def test_spmm_with_hints_is_bit_identical(oracle_cpu, dtype):
                               spmm_abs_scale(srp, scol, sval, B.numpy()), "hinted spmm")
 
 
+def test_hints_are_ignored_for_widths_without_a_hinted_kernel():
+    """The marks act on the 512-byte tile only: with a narrower or a ragged width the hinted entry
+    points run the plain kernels and give the same bits."""
+    A = W.rmat(scale=18)
+    d, meta = gpu_inputs(A)
+    hot = capi.hot_columns(d.col, A.n, 512, budget_bytes=10000 * 512)
+    assert hot is not None
+    for n in (32, 64, 132, 20):
+        Bd = W.dense(A.n, n, seed=n).cuda()
+        plain = capi.spmm(meta, d.row_ptr, d.col, d.val, Bd)
+        hinted = capi.spmm(meta, d.row_ptr, d.col, d.val, Bd, hot=hot)
+        torch.cuda.synchronize()
+        assert torch.equal(plain, hinted), n
+
+
 def test_bitmap_with_a_cleared_flag_is_harmless_through_the_c_abi(oracle_cpu):
     """A caller that hands a bitmap straight to rode_spmm_f32_hot without reading its flag
     word: when the library judged the marks useless (flag 0) the kernel gives every row the
